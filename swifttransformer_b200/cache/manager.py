@@ -121,13 +121,20 @@ class PagedGroup:
         limits = [n for n in (self.spec.window, self.spec.block) if n is not None]
         return min(limits) if limits else None
 
+    @property
+    def _kept_pages(self) -> int:
+        """Leading logical pages that stay whatever the window does (they hold keys every query sees)."""
+        if self.spec.window is None or self.spec.keep_first <= 0:
+            return 0
+        return (self.spec.keep_first + self.page_size - 1) // self.page_size
+
     def peak_pages(self, end: int, portion: int) -> int:
         """The most pages a request holds at any time while it is brought to ``end`` tokens in portions of at
         most ``portion``: all of them, or what a window and one portion span."""
         total = (end + self.page_size - 1) // self.page_size
         if self._reach is None:
             return total
-        return min(total, (self._reach - 1 + portion + self.page_size - 1) // self.page_size + 1)
+        return min(total, (self._reach - 1 + portion + self.page_size - 1) // self.page_size + 1 + self._kept_pages)
 
     def missing(self, slot: int, start: int, end: int) -> List[int]:
         """Logical pages that positions start..end-1 need and the slot does not hold."""
@@ -137,7 +144,9 @@ class PagedGroup:
         last = (end - 1) // self.page_size
         if last >= self.max_pages_per_seq:
             raise ValueError(f"a request of {end} tokens needs more than {self.max_pages_per_seq} pages")
-        return [j for j in range(self._first_needed_page(start), last + 1) if j not in held]
+        first = self._first_needed_page(start)
+        # (a request's kept first pages are written when it starts; a later portion never asks for them again)
+        return [j for j in range(first, last + 1) if j not in held]
 
     def reserve(self, slot: int, start: int, end: int) -> bool:
         need = self.missing(slot, start, end)
@@ -162,7 +171,8 @@ class PagedGroup:
         if self._reach is None:
             return 0
         first = self._first_needed_page(length)
-        gone = [j for j in self.pages[slot] if j < first]
+        kept = self._kept_pages
+        gone = [j for j in self.pages[slot] if kept <= j < first]
         self._release(slot, gone)
         return len(gone)
 

@@ -1,0 +1,282 @@
+// The gated delta rule: a linear recurrence whose state is corrected towards each token's value.
+//
+// Per value head h (G query/key heads serve H value heads: g = h / (H / G)), with S [dim, vd] zero when a
+// request starts:
+//
+//   q, k, v  = silu(conv(projection))            short causal convolution over time, one filter per channel
+//   q <- q / sqrt(sum q^2 + 1e-6) * dim^(-1/2),  k <- k / sqrt(sum k^2 + 1e-6)          per head
+//   beta     = sigmoid(b)                                                              per head
+//   decay_c  = exp(-exp(A_log_h) * softplus(sum_r a1_r * W_a2[h * dim + c, r] + dt_bias[h * dim + c]))
+//   S <- diag(decay) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+//   out      = out_scale * o / sqrt(mean(o^2) + eps) * w * sigmoid(sum_r g1_r * W_g2[h * vd + e, r])
+//
+// Three kernels.  delta_prepare turns a token's row of the float projection [q | k | v | b | a1 | g1] into a
+// float row [q (G*dim) | k (G*dim) | v (H*vd) | decay (H*dim) | beta (H)]; delta_scan walks each request's
+// tokens with the state's columns in registers (a column of S evolves on its own: its dot products with k and q
+// are sums over dim, shared by the L lanes that hold the column); delta_output norms and gates each head's o.
+// Everything here is float arithmetic; only the low-rank matrices and the result are in the storage type.
+//
+// Since (decay S + k u^T)^T q = (decay S)^T q + u (k . q), both dot products of a token are taken from the
+// decayed state in one pass of shuffles.
+#include "common.cuh"
+
+#define DR_MAX_TAPS 8
+#define DR_PREP_THREADS 256
+#define DR_UNIT_PASSES 8      // a warp's lanes cover a head of up to 32 * DR_UNIT_PASSES channels
+
+struct DeltaShape {
+    int H, G, dim, vd;            // value heads, query/key heads, key size, value size
+    int q_off, k_off, v_off, b_off, a_off, g_off;   // columns of the projection
+    int rank_a, rank_g;
+    // columns of a prepared row
+    __host__ __device__ int pq() const { return 0; }
+    __host__ __device__ int pk() const { return G * dim; }
+    __host__ __device__ int pv() const { return 2 * G * dim; }
+    __host__ __device__ int pd() const { return 2 * G * dim + H * vd; }
+    __host__ __device__ int pb() const { return 2 * G * dim + H * vd + H * dim; }
+    __host__ __device__ int row() const { return 2 * G * dim + H * vd + H * dim + H; }
+};
+
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float siluf_(float z) { return z / (1.f + expf(-z)); }
+
+// conv_w: float [2*G*dim + H*vd, taps] in the projection's order q | k | v; state: [slots, taps-1, channels]
+// float, the last taps-1 projected rows of every request (read here; with move_state, in steps where every request
+// brings one token, also moved on here: the thread that reads a channel's state is the only one that writes it).
+template <typename TW>
+__global__ void __launch_bounds__(DR_PREP_THREADS)
+delta_prepare_kernel(const float* __restrict__ proj, int ld, DeltaShape sh, const float* __restrict__ conv_w,
+                     float* __restrict__ state, int move_state, int taps, const TW* __restrict__ w_a2,
+                     const float* __restrict__ a_log, const float* __restrict__ dt_bias, float* __restrict__ prep,
+                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                     const int* __restrict__ q_start, const int* __restrict__ slots) {
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos < 0) return;
+    const int b = seq_of_token[t];
+    const int i = t - q_start[b];                         // the token's place in its portion
+    const int H = sh.H, G = sh.G, dim = sh.dim, vd = sh.vd;
+    const int channels = 2 * G * dim + H * vd;
+    const int keep = taps - 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const float* row = proj + (size_t)t * ld;
+    float* st = state + (size_t)slots[b] * keep * channels;
+    float* dst = prep + (size_t)t * sh.row();
+    const int units = 2 * G + H;
+    for (int u = blockIdx.y * nwarp + warp; u < units; u += nwarp * gridDim.y) {
+        const bool is_v = u >= 2 * G;
+        const int width = is_v ? vd : dim;
+        const int ch0 = is_v ? 2 * G * dim + (u - 2 * G) * vd : u * dim;     // q heads, then k heads, then v heads
+        float x[DR_UNIT_PASSES];
+        float ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < DR_UNIT_PASSES; ++r) {
+            x[r] = 0.f;
+            const int e = lane + 32 * r;
+            if (e >= width) continue;
+            const int c = ch0 + e;
+            // the projection's columns q_off.. hold q | k | v in this order
+            float y = 0.f, vv[DR_MAX_TAPS];
+            for (int j = 0; j < taps; ++j) {
+                const int back = keep - j;
+                float v;
+                if (back <= i) v = __ldcg(row - (size_t)back * ld + sh.q_off + c);
+                else v = __ldcg(st + (size_t)(keep - (back - i)) * channels + c);    // zero before the request's start
+                vv[j] = v;
+                y = fmaf(conv_w[(size_t)c * taps + j], v, y);
+            }
+            if (move_state)
+                for (int j = 0; j < keep; ++j) st[(size_t)j * channels + c] = vv[j + 1];
+            y = siluf_(y);
+            x[r] = y;
+            ss = fmaf(y, y, ss);
+        }
+        float mult = 1.f;
+        if (!is_v) {
+            ss = warp_sum(ss);
+            mult = rsqrtf(ss + 1e-6f);
+            if (u < G) mult *= rsqrtf((float)dim);
+        }
+#pragma unroll
+        for (int r = 0; r < DR_UNIT_PASSES; ++r) {
+            const int e = lane + 32 * r;
+            if (e < width) dst[ch0 + e] = x[r] * mult;       // the prepared row starts with q | k | v as well
+        }
+    }
+    if (blockIdx.y == 0) {
+        for (int h = threadIdx.x; h < H; h += blockDim.x)
+            dst[sh.pb() + h] = 1.f / (1.f + expf(-__ldcg(row + sh.b_off + h)));
+    }
+    // decays: the low-rank step size, one thread per (head, key channel)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H * dim; c += blockDim.x * gridDim.y) {
+        float z = 0.f;
+        const TW* w = w_a2 + (size_t)c * sh.rank_a;
+        for (int r = 0; r < sh.rank_a; ++r) z = fmaf(__ldcg(row + sh.a_off + r), to_f32(w[r]), z);
+        const float dt = softplusf_(z + dt_bias[c]);
+        dst[sh.pd() + c] = expf(-expf(a_log[c / dim]) * dt);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The recurrence.  grid (requests of the step, H, column groups); a block of DS_THREADS threads holds
+// DS_THREADS / L columns of one head's state, L lanes per column with R consecutive rows each (dim <= L * R).
+#define DS_THREADS 128
+
+template <int L, int R>
+__global__ void __launch_bounds__(DS_THREADS)
+delta_scan_kernel(const float* __restrict__ prep, DeltaShape sh, float* __restrict__ state, int write_state,
+                  float* __restrict__ o_out, const int* __restrict__ positions, const int* __restrict__ q_start,
+                  const int* __restrict__ slots) {
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int first = q_start[b], n = q_start[b + 1] - first;
+    if (n <= 0 || positions[first] < 0) return;            // padding of a fixed-shape step
+    const int H = sh.H, dim = sh.dim, vd = sh.vd;
+    const int g = h / (H / sh.G);
+    const int sub = threadIdx.x % L;
+    const int col = blockIdx.z * (DS_THREADS / L) + threadIdx.x / L;
+    const bool live = col < vd;
+    const int d0 = sub * R;
+    float* S = state + (((size_t)slots[b] * H + h) * dim) * vd + col;
+    float s[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) s[r] = (live && d0 + r < dim) ? S[(size_t)(d0 + r) * vd] : 0.f;
+    const int row_len = sh.row();
+    const float* p = prep + (size_t)first * row_len;
+    float kq[R], qq[R], dd[R], v, beta;
+    auto fetch = [&](const float* row) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const bool in = d0 + r < dim;
+            kq[r] = in ? __ldcg(row + sh.pk() + g * dim + d0 + r) : 0.f;
+            qq[r] = in ? __ldcg(row + sh.pq() + g * dim + d0 + r) : 0.f;
+            dd[r] = in ? __ldcg(row + sh.pd() + h * dim + d0 + r) : 0.f;
+        }
+        v = live ? __ldcg(row + sh.pv() + h * vd + col) : 0.f;
+        beta = __ldcg(row + sh.pb() + h);
+    };
+    fetch(p);
+    for (int t = 0; t < n; ++t) {
+        float k_[R], q_[R];
+        float sk = 0.f, sq = 0.f, kdq = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            k_[r] = kq[r];
+            q_[r] = qq[r];
+            s[r] *= dd[r];
+            sk = fmaf(s[r], k_[r], sk);
+            sq = fmaf(s[r], q_[r], sq);
+            kdq = fmaf(k_[r], q_[r], kdq);
+        }
+        const float v_now = v, beta_now = beta;
+        if (t + 1 < n) fetch(p + (size_t)(t + 1) * row_len);      // the next token's row is on its way meanwhile
+#pragma unroll
+        for (int o = L / 2; o > 0; o >>= 1) {
+            sk += __shfl_xor_sync(0xffffffffu, sk, o);
+            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            kdq += __shfl_xor_sync(0xffffffffu, kdq, o);
+        }
+        const float u = beta_now * (v_now - sk);
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[r] = fmaf(k_[r], u, s[r]);
+        if (live && sub == 0) o_out[(size_t)(first + t) * H * vd + h * vd + col] = fmaf(u, kdq, sq);
+    }
+    if (write_state && live) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            if (d0 + r < dim) S[(size_t)(d0 + r) * vd] = s[r];
+    }
+}
+
+// out[t, h, e] = out_scale * o / sqrt(mean_e o^2 + eps) * norm_w[e] * sigmoid(sum_r g1[t, r] * W_g2[h * vd + e, r])
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_output_kernel(const float* __restrict__ o, const float* __restrict__ proj, int ld, DeltaShape sh,
+                    const T* __restrict__ w_g2, const float* __restrict__ norm_w, float eps, float out_scale,
+                    T* __restrict__ out, const int* __restrict__ positions) {
+    __shared__ float scratch[32];
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int t = blockIdx.x, h = blockIdx.y;
+    if (positions[t] < 0) return;
+    const int vd = sh.vd;
+    const float* orow = o + ((size_t)t * sh.H + h) * vd;
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < vd; e += blockDim.x) {
+        const float x = __ldcg(orow + e);
+        ss = fmaf(x, x, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)vd + eps) * out_scale;
+    const float* g1 = proj + (size_t)t * ld + sh.g_off;
+    for (int e = threadIdx.x; e < vd; e += blockDim.x) {
+        float z = 0.f;
+        const T* w = w_g2 + (size_t)(h * vd + e) * sh.rank_g;
+        for (int r = 0; r < sh.rank_g; ++r) z = fmaf(__ldcg(g1 + r), to_f32(w[r]), z);
+        out[((size_t)t * sh.H + h) * vd + e] = from_f32<T>(__ldcg(orow + e) * inv * norm_w[e] / (1.f + expf(-z)));
+    }
+}
+
+ST_EXPORT long long st_delta_rule_scratch_floats(int n_tokens, int H, int G, int dim, int vd) {
+    return (long long)n_tokens * ((long long)2 * G * dim + (long long)H * vd + (long long)H * dim + H + (long long)H * vd);
+}
+
+// proj: float [n_tokens, ld]; w_a2 [H*dim, rank_a], w_g2 [H*vd, rank_g] in the storage type `dtype`, as is out
+// [n_tokens, H*vd]; conv_state float [slots, taps-1, 2*G*dim + H*vd]; state float [slots, H, dim, vd];
+// scratch: float, st_delta_rule_scratch_floats elements.  write_state == 0: the states are read, not moved on.
+ST_EXPORT int st_delta_rule(const float* proj, int ld, int q_off, int b_off, int a_off, int g_off, int rank_a,
+                            int rank_g, const float* conv_w, int taps, float* conv_state, const void* w_a2,
+                            const float* a_log, const float* dt_bias, const void* w_g2, const float* norm_w, float eps,
+                            float out_scale, float* state, int write_state, int single_tokens, float* scratch,
+                            void* out, const int* positions, const int* seq_of_token, const int* q_start,
+                            const int* slots, int n_tokens, int n_seqs, int H, int G, int dim, int vd, int dtype,
+                            void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vd <= 0 || taps < 1 || rank_a <= 0 || rank_g <= 0) return ST_ERR_BAD_ARG;
+    if (taps > DR_MAX_TAPS || dim > 32 * DR_UNIT_PASSES || vd > 32 * DR_UNIT_PASSES) return ST_ERR_TOO_LARGE;
+    if (dtype != 0 && dtype != 1) return ST_ERR_BAD_DTYPE;
+    DeltaShape sh;
+    sh.H = H; sh.G = G; sh.dim = dim; sh.vd = vd;
+    sh.q_off = q_off; sh.k_off = q_off + G * dim; sh.v_off = q_off + 2 * G * dim;
+    sh.b_off = b_off; sh.a_off = a_off; sh.g_off = g_off; sh.rank_a = rank_a; sh.rank_g = rank_g;
+    cudaStream_t s = (cudaStream_t)stream;
+    float* prep = scratch;
+    float* o = scratch + (size_t)n_tokens * sh.row();
+    const int move = single_tokens && write_state && taps > 1;
+    int rc;
+    {
+        const int units = 2 * G + H;
+        int gy = (units + 7) / 8;
+        if (gy > 16) gy = 16;
+        dim3 grid(n_tokens, gy);
+        if (dtype == 0)
+            rc = st_launch_pdl("delta_prepare", delta_prepare_kernel<float>, grid, dim3(DR_PREP_THREADS), 0, s, proj, ld, sh,
+                               conv_w, conv_state, move, taps, (const float*)w_a2, a_log, dt_bias, prep, positions,
+                               seq_of_token, q_start, slots);
+        else
+            rc = st_launch_pdl("delta_prepare", delta_prepare_kernel<bf16>, grid, dim3(DR_PREP_THREADS), 0, s, proj, ld, sh,
+                               conv_w, conv_state, move, taps, (const bf16*)w_a2, a_log, dt_bias, prep, positions,
+                               seq_of_token, q_start, slots);
+        if (rc) return rc;
+    }
+    {
+#define DS_LAUNCH(L, R)                                                                                              \
+    rc = st_launch_pdl("delta_scan", delta_scan_kernel<L, R>, dim3(n_seqs, H, (vd + DS_THREADS / L - 1) / (DS_THREADS / L)), \
+                       dim3(DS_THREADS), 0, s, (const float*)prep, sh, state, write_state, o, positions, q_start, slots)
+        if (dim <= 32) DS_LAUNCH(8, 4);
+        else if (dim <= 64) DS_LAUNCH(8, 8);
+        else if (dim <= 128) DS_LAUNCH(8, 16);
+        else DS_LAUNCH(32, 8);
+#undef DS_LAUNCH
+        if (rc) return rc;
+    }
+    dim3 grid(n_tokens, H);
+    if (dtype == 0)
+        return st_launch_pdl("delta_output", delta_output_kernel<float>, grid, dim3(128), 0, s, (const float*)o, proj, ld, sh,
+                             (const float*)w_g2, norm_w, eps, out_scale, (float*)out, positions);
+    return st_launch_pdl("delta_output", delta_output_kernel<bf16>, grid, dim3(128), 0, s, (const float*)o, proj, ld, sh,
+                         (const bf16*)w_g2, norm_w, eps, out_scale, (bf16*)out, positions);
+}

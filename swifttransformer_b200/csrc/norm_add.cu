@@ -118,3 +118,39 @@ ST_EXPORT int st_gated_act(const void* gu, void* out, int n_rows, int inner, int
 #undef GA_LAUNCH
     return ST_ERR_BAD_DTYPE;
 }
+
+// The gated unit with limits, from the fused gate | up product gu [rows, 2 * inner] and its bias (float
+// [2 * inner] or null):  g = min(gate + b_g, limit), u = clamp(up + b_u, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + shift).  limit <= 0: no limits.
+template <typename T>
+__global__ void gated_clamped_act_kernel(const T* __restrict__ gu, const float* __restrict__ bias, T* __restrict__ out,
+                                         int inner, size_t total, float limit, float alpha, float shift) {
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t r = i / inner, j = i % inner;
+        const T* row = gu + r * 2 * inner;
+        float g = load1_cg(row + j), u = load1_cg(row + inner + j);
+        if (bias) { g += bias[j]; u += bias[inner + j]; }
+        if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        out[i] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + shift));
+    }
+}
+
+ST_EXPORT int st_gated_clamped_act(const void* gu, const float* bias, void* out, int n_rows, int inner, float limit,
+                                   float alpha, float shift, int dtype, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (inner <= 0) return ST_ERR_BAD_ARG;
+    const size_t total = (size_t)n_rows * inner;
+    int grid = (int)((total + 255) / 256);
+    if (grid > st_sm_count() * 16) grid = st_sm_count() * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == 0)
+        return st_launch_pdl("gated_clamped", gated_clamped_act_kernel<float>, dim3(grid), dim3(256), 0, s, (const float*)gu,
+                             bias, (float*)out, inner, total, limit, alpha, shift);
+    if (dtype == 1)
+        return st_launch_pdl("gated_clamped", gated_clamped_act_kernel<bf16>, dim3(grid), dim3(256), 0, s, (const bf16*)gu,
+                             bias, (bf16*)out, inner, total, limit, alpha, shift);
+    return ST_ERR_BAD_DTYPE;
+}

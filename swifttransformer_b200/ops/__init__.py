@@ -1113,3 +1113,114 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor, top_k: torch.Tensor
 def uniform(seed: int, counter: int) -> float:
     """The uniform number in [0,1) that `sample` uses for (seed, counter); computed on the host."""
     return float(lib().st_uniform_host(seed, counter))
+
+
+# ------------------------------------------------------------ grouped attention (keys and values of own sizes)
+def _gqa_pool(pool: torch.Tensor, layer: int, nkv: int, dim: int, vd: int, page_size: int):
+    """(page stride, offset of the entry) in elements, for a pool [pages, entries, nkv * page_size * (dim + vd)]."""
+    assert pool.dim() == 3 and pool.is_contiguous() and pool.shape[2] == nkv * page_size * (dim + vd)
+    return ctypes.c_longlong(pool.stride(0)), ctypes.c_longlong(layer * pool.stride(1))
+
+
+def gqa_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bias: Optional[torch.Tensor],
+                inv_freq: Optional[torch.Tensor], rot_dims: int, temp_coef: float, temp_every: int,
+                q_out: torch.Tensor, pool: torch.Tensor, layer: int, positions: torch.Tensor,
+                seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int,
+                dim: int, vd: int, page_size: int, status: Optional[torch.Tensor], write_kv: bool = True) -> None:
+    """Queries, keys and values of a step from the fused projection ``proj`` [tokens, columns] (queries at column
+    q_off, keys at k_off, values at v_off): plus ``bias`` (float32, one number per column of proj, or None); the
+    first ``rot_dims`` dimensions of every query and key head rotated by position in the halves layout; queries
+    times 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1); queries to ``q_out`` [tokens, nh * dim], keys and
+    values into their pages (``write_kv`` False: queries only)."""
+    assert proj.is_contiguous() and q_out.is_contiguous() and q_out.shape == (proj.shape[0], nh * dim)
+    assert proj.dtype == q_out.dtype == pool.dtype
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == proj.shape[1]
+    stride, off = _gqa_pool(pool, layer, nkv, dim, vd, page_size)
+    _check(lib().st_gqa_prepare(_p(proj), proj.shape[1], q_off, k_off, v_off, _p(bias), _p(inv_freq), rot_dims,
+                                _f(temp_coef), temp_every, _p(q_out), _p(pool), stride, off, _p(positions),
+                                _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1], proj.shape[0], nh,
+                                nkv, dim, vd, page_size, int(write_kv), _p(status), _dt(proj), _stream()), "gqa_prepare")
+
+
+def _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink, gate, gate_off, out_scale):
+    stride, off = _gqa_pool(pool, layer, nkv, dim, vd, page_size)
+    gate_ptr = None
+    if gate is not None:
+        assert gate.is_contiguous() and gate.dtype == pool.dtype
+        gate_ptr = ctypes.c_void_p(gate.data_ptr() + gate_off * gate.element_size())
+    return stride, off, gate_ptr, ctypes.c_longlong(gate.shape[1] if gate is not None else 0)
+
+
+def gqa_attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
+                        seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int,
+                        dim: int, vd: int, page_size: int, scale: float, window: int, keep_first: int,
+                        sink: Optional[float], gate: Optional[torch.Tensor], gate_off: int, out_scale: float,
+                        status: Optional[torch.Tensor] = None, items: Optional[torch.Tensor] = None,
+                        n_items: Optional[int] = None) -> torch.Tensor:
+    """Grouped attention of every token of the step (or of those ``items`` lists) over the paged cache, in float
+    arithmetic for either storage type.  ``window`` 0: all keys up to the query; else the last ``window`` keys and
+    the request's first ``keep_first``.  ``sink``: a logit that joins the softmax's denominator (None: none).
+    ``gate`` [tokens, columns]: the head's result is multiplied by sigmoid of its columns from ``gate_off`` on."""
+    assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
+    stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink,
+                                               gate, gate_off, out_scale)
+    n = q.shape[0] if items is None else (n_items if n_items is not None else items.numel())
+    _check(lib().st_gqa_attention_plain(_p(q), _p(pool), stride, off, _p(out), _p(items), _p(positions),
+                                        _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1], n, nh, nkv,
+                                        dim, vd, page_size, _f(scale), window, keep_first, int(sink is not None),
+                                        _f(sink or 0.0), gate_ptr, gate_ld, _f(out_scale), _p(status), _dt(q),
+                                        _stream()), "gqa_attention_plain")
+    return out
+
+
+# ------------------------------------------------------------ the gated delta rule
+def delta_rule_scratch(n_tokens: int, H: int, G: int, dim: int, vd: int) -> int:
+    lib().st_delta_rule_scratch_floats.restype = ctypes.c_longlong
+    return int(lib().st_delta_rule_scratch_floats(n_tokens, H, G, dim, vd))
+
+
+def delta_rule(proj: torch.Tensor, b_off: int, a_off: int, g_off: int, conv_w: torch.Tensor, conv_state: torch.Tensor,
+               w_a2: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, w_g2: torch.Tensor, norm_w: torch.Tensor,
+               eps: float, out_scale: float, state: torch.Tensor, write_state: bool, single_tokens: bool,
+               scratch: torch.Tensor, out: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+               q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, H: int, G: int, dim: int, vd: int) -> torch.Tensor:
+    """The gated delta rule over each request's tokens of the step, from the float32 projection ``proj`` [tokens,
+    columns] = q (G * dim) | k (G * dim) | v (H * vd) from column 0, write strengths at b_off (H), the low-rank
+    inputs of the decays at a_off and of the output gates at g_off.  ``conv_w`` float32 [channels, taps], the
+    filters of q | k | v; ``conv_state`` float32 [slots, taps - 1, channels] is read and, when every request brings
+    one token, moved on (else ``conv_state_update`` follows); ``state`` float32 [slots, H, dim, vd] is read and
+    moved on.  out [tokens, H * vd] in the type of ``w_a2`` / ``w_g2``."""
+    assert proj.dtype == torch.float32 and proj.is_contiguous() and out.is_contiguous()
+    assert out.shape == (proj.shape[0], H * vd) and w_a2.dtype == w_g2.dtype == out.dtype
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dim, vd)
+    channels = 2 * G * dim + H * vd
+    taps = conv_w.shape[1]
+    assert conv_w.dtype == torch.float32 and conv_w.shape[0] == channels and conv_w.is_contiguous()
+    assert conv_state.dtype == torch.float32 and conv_state.shape[1:] == (taps - 1, channels)
+    assert w_a2.is_contiguous() and w_g2.is_contiguous() and w_a2.shape[0] == H * dim and w_g2.shape[0] == H * vd
+    assert scratch.dtype == torch.float32 and scratch.numel() >= delta_rule_scratch(proj.shape[0], H, G, dim, vd)
+    _check(lib().st_delta_rule(_p(proj), proj.shape[1], 0, b_off, a_off, g_off, w_a2.shape[1], w_g2.shape[1],
+                               _p(conv_w), taps, _p(conv_state), _p(w_a2), _p(a_log), _p(dt_bias), _p(w_g2),
+                               _p(norm_w), _f(eps), _f(out_scale), _p(state), int(write_state), int(single_tokens),
+                               _p(scratch), _p(out), _p(positions), _p(seq_of_token), _p(q_start), _p(slots),
+                               proj.shape[0], n_seqs, H, G, dim, vd, _dt(out), _stream()), "delta_rule")
+    return out
+
+
+def gated_clamped_act(gu: torch.Tensor, bias: Optional[torch.Tensor], limit: float, alpha: float,
+                      shift: float) -> torch.Tensor:
+    """g * sigmoid(alpha * g) * (u + shift) with g = min(gate + b, limit), u = clamp(up + b, -limit, limit) for the
+    fused gate | up product gu [rows, 2 * inner] and its float32 bias [2 * inner] (None: none; limit <= 0: none)."""
+    assert gu.is_contiguous() and gu.shape[1] % 2 == 0
+    inner = gu.shape[1] // 2
+    out = torch.empty((gu.shape[0], inner), dtype=gu.dtype, device=gu.device)
+    _check(lib().st_gated_clamped_act(_p(gu), _p(bias), _p(out), gu.shape[0], inner, _f(limit), _f(alpha), _f(shift),
+                                      _dt(gu), _stream()), "gated_clamped_act")
+    return out
+
+
+def gqa_attention_fast_applies(q: torch.Tensor, dim: int, vd: int) -> bool:
+    """Whether the bfloat16 kernels (query tiles on the tensor cores, single tokens with 16-byte accesses) take
+    these sizes."""
+    return False

@@ -3,13 +3,16 @@ from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Del
                    PagedKVSpec, Part, Registry, StateSpec)
 from .block import Block, NormAfterBlock, ParallelBlock, PostNormBlock, PreNormBlock, ReentryBlock, ResidualStream
 from .conv import InputConv
+from .delta_rule import GatedDeltaRule
 from .diff_attention import DifferentialAttention
 from .embedding import Embedding, OutputHead
-from .ffn import DenseFFN, GatedFFN
+from .ffn import ClampedGatedFFN, DenseFFN, GatedFFN
+from .grouped_attention import GroupedAttention
 from .hgrn2 import HGRN2
 from .latent_attention import LatentAttention
 from .moe import RoutedExperts
 from .norm import LayerNorm, NoNorm, Norm, OffsetRMSNorm, RMSNorm, ScalarRMSNorm
+from .side_by_side import SideBySide
 from .position import LearnedPositions, NoPositions, PositionEncoding, RotaryHalves, RotaryPairs
 
 __all__ = ["Attention", "BLOCKS", "Block", "Delta", "DenseFFN", "Embedding", "FEED_FORWARDS", "FeedForward",
@@ -17,4 +20,4 @@ __all__ = ["Attention", "BLOCKS", "Block", "Delta", "DenseFFN", "Embedding", "FE
            "OutputHead", "POSITION_ENCODINGS", "PagedKVSpec", "Part", "PositionEncoding", "PostNormBlock",
            "PreNormBlock", "RMSNorm", "Registry", "ResidualStream", "StateSpec", "paged_attention",
            "DifferentialAttention", "GatedFFN", "HGRN2", "InputConv", "NormAfterBlock", "RotaryPairs", "ScalarRMSNorm",
-           "LatentAttention", "OffsetRMSNorm", "ParallelBlock", "ReentryBlock", "RotaryHalves", "RoutedExperts"]
+           "LatentAttention", "OffsetRMSNorm", "ClampedGatedFFN", "GatedDeltaRule", "GroupedAttention", "SideBySide", "ParallelBlock", "ReentryBlock", "RotaryHalves", "RoutedExperts"]

@@ -60,12 +60,15 @@ class PagedKVSpec:
     the keys [kv_head][position][head_dim] followed by the values [kv_head][position][value_dim]; with
     ``value_dim`` None it is [pages, entries, 2, kv_heads, page_size, head_dim].
     ``block``: the mask is block-diagonal, a query sees only the keys of its own block of ``block``
-    positions (counted from position 0): pages that lie before the block of the next query are given back."""
+    positions (counted from position 0): pages that lie before the block of the next query are given back.
+    ``keep_first``: with a window, every query also sees the request's first ``keep_first`` keys: the pages that
+    hold them stay while the window moves on."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
     block: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclasses.dataclass(frozen=True)

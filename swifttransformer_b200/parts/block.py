@@ -66,6 +66,16 @@ class Block(Part):
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
+    """r = x + mixer(norm1(x)); x' = r + ffn(norm2(r)).  The feed-forward (and norm2 with it) may be absent."""
+
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], norm1: Norm, norm2: Optional[Norm] = None):
+        if (feed_forward is None) != (norm2 is None):
+            raise ValueError("a block has a second norm exactly when it has a feed-forward")
+        super().__init__(mixer, feed_forward, norm1, norm2)
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
     def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
         # A sub-layer that can take its norm and its residual sum into its own kernels does so (steps of a
         # few tokens, where every kernel less shortens the chain); otherwise norm kernel, sub-layer, and the
@@ -78,6 +88,9 @@ class PreNormBlock(Block):
             pending = self.mixer.forward(h, ctx, cache)
         else:
             pending = None if done is True else done
+        if self.feed_forward is None:
+            stream.pending, stream.act = pending, None
+            return
         done = self.feed_forward.forward_into_residual(x, self.norm2, ctx, pending) if low else False
         if done is False:
             h = self.norm2.apply(x, pending, act_dtype=stream.act_dtype)

@@ -97,3 +97,42 @@ class GatedFFN(FeedForward):
 
     def param_bytes(self) -> int:
         return (self.w_gu.numel() + self.w_down.numel()) * self.w_gu.element_size()
+
+
+@FEED_FORWARDS.register("gated_clamped")
+class ClampedGatedFFN(FeedForward):
+    """z = down(g * sigmoid(alpha * g) * (u + shift)) + b_down with g = min(gate h + b_gate, limit) and
+    u = clamp(up h + b_up, -limit, limit).  The gate and up matrices are stacked at load time so that one product
+    gives both; their biases, the limits and the unit are one kernel.  ``bias``: whether the three projections have
+    biases (a projection's bias is its name + ``bias_suffix``)."""
+
+    def __init__(self, hidden: int, inner: int, limit: float, gate_name: str, up_name: str, down_name: str,
+                 alpha: float = 1.0, shift: float = 0.0, bias: bool = True, bias_suffix: str = ".b"):
+        self.hidden, self.inner, self.limit, self.alpha, self.shift = hidden, inner, float(limit), float(alpha), float(shift)
+        self.gate_name, self.up_name, self.down_name, self.bias, self.suffix = gate_name, up_name, down_name, bias, bias_suffix
+        self.w_gu = self.b_gu = self.w_down = self.b_down = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        specs = [ParamSpec(self.gate_name, (self.inner, self.hidden), MATRIX),
+                 ParamSpec(self.up_name, (self.inner, self.hidden), MATRIX),
+                 ParamSpec(self.down_name, (self.hidden, self.inner), MATRIX)]
+        if self.bias:
+            specs += [ParamSpec(self.gate_name + self.suffix, (self.inner,), VECTOR),
+                      ParamSpec(self.up_name + self.suffix, (self.inner,), VECTOR),
+                      ParamSpec(self.down_name + self.suffix, (self.hidden,), VECTOR)]
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_gu = torch.cat([tensors.pop(self.gate_name), tensors.pop(self.up_name)], dim=0).contiguous()
+        self.w_down = tensors[self.down_name]
+        if self.bias:
+            self.b_gu = torch.cat([tensors.pop(self.gate_name + self.suffix), tensors.pop(self.up_name + self.suffix)],
+                                  dim=0).contiguous()
+            self.b_down = tensors[self.down_name + self.suffix]
+
+    def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
+        u = ops.gated_clamped_act(ops.linear(h, self.w_gu), self.b_gu, self.limit, self.alpha, self.shift)
+        return Delta(ops.linear(u, self.w_down), self.b_down)
+
+    def param_bytes(self) -> int:
+        return (self.w_gu.numel() + self.w_down.numel()) * self.w_gu.element_size()

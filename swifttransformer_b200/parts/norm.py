@@ -69,14 +69,20 @@ class LayerNorm(Norm):
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
+    """y = x / sqrt(mean(x^2) + eps) * w.  The weight is the tensor ``name`` when that is given, else
+    ``prefix`` + ".weight"."""
     kind = "rmsnorm"
 
+    def __init__(self, width: int, eps: float = 1e-5, affine: bool = True, prefix: str = "", name: str = ""):
+        super().__init__(width, eps, affine, prefix)
+        self.name = name or (prefix + ".weight")
+
     def param_specs(self) -> List[ParamSpec]:
-        return [ParamSpec(self.prefix + ".weight", (self.width,), GAIN)] if self.affine else []
+        return [ParamSpec(self.name, (self.width,), GAIN)] if self.affine else []
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         if self.affine:
-            self.gamma = tensors[self.prefix + ".weight"]
+            self.gamma = tensors[self.name]
 
     def param_bytes(self) -> int:
         return 4 * self.width if self.affine else 0

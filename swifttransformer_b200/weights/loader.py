@@ -68,8 +68,9 @@ def load_named_tensors(
             continue
         f, raw = found[s.name]
         info = f.tensors[raw]
-        if tuple(info.shape) != tuple(s.shape):
-            wrong.append(f"{s.name}: file has {list(info.shape)}, model wants {list(s.shape)}")
+        if not s.fits(info.shape):
+            wrong.append(f"{s.name}: file has {list(info.shape)}, model wants "
+                         f"{[n if n >= 0 else 'any' for n in s.shape]}")
         elif info.dtype.is_floating_point == (s.role == "int_table"):
             wrong.append(f"{s.name}: file has {info.dtype}, model wants "
                          f"{'an integer' if s.role == 'int_table' else 'a floating-point'} tensor")

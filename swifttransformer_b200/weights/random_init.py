@@ -29,8 +29,8 @@ def _one(spec: ParamSpec, index: int, seed: int, std: float, device) -> torch.Te
     gen = torch.Generator(device=device)
     gen.manual_seed((int(seed) * 1000003 + index * 7919 + 12345) % (2 ** 63 - 1))
     if spec.role == INT_TABLE:
-        return torch.randint(0, 2 ** 15, spec.shape, generator=gen, device=device, dtype=torch.int32)
-    t = torch.randn(spec.shape, generator=gen, device=device, dtype=torch.float32)
+        return torch.randint(0, 2 ** 15, spec.made_shape(), generator=gen, device=device, dtype=torch.int32)
+    t = torch.randn(spec.made_shape(), generator=gen, device=device, dtype=torch.float32)
     if spec.role == GAIN:
         t.mul_(GAIN_STD).add_(1.0)
     else:

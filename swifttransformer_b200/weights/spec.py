@@ -17,12 +17,22 @@ INT_TABLE = "int_table"  # integer lookup table: int32
 @dataclasses.dataclass(frozen=True)
 class ParamSpec:
     name: str                     # tensor name in the checkpoint
+    # a negative size -n stands for "whatever the checkpoint has" (a size no configuration key gives, such as
+    # the rank of a low-rank pair); n is the size the tensor gets when weights are made at random
     shape: Tuple[int, ...]
     role: str = MATRIX
     # an optional tensor may be absent from the checkpoint (e.g. an output
     # matrix that is tied to the embedding table); `tied_to` names the tensor
     # whose values it then takes.
     tied_to: Optional[str] = None
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w < 0 or w == h for w, h in zip(self.shape, shape))
+
+    def made_shape(self) -> Tuple[int, ...]:
+        """The shape of the tensor when it is made at random."""
+        return tuple(abs(n) for n in self.shape)
 
     def storage_dtype(self, compute_dtype: torch.dtype, stored: Optional[torch.dtype] = None) -> torch.dtype:
         if self.role in (VECTOR, GAIN):
