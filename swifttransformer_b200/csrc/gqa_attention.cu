@@ -213,3 +213,182 @@ ST_EXPORT int st_gqa_attention_plain(const void* q, const void* pool, long long 
                              scale, mask, has_sink, sink, epi, status);
     return ST_ERR_BAD_DTYPE;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Single tokens and short portions in bfloat16: one block per (token, key/value head) serves all REP query heads
+// of the group, so a key or value row is fetched once for them.  The seen keys (the kept first ones, then the
+// window up to the query) are numbered in one run; warp w takes keys w*GS_BATCH .. of every GS_WARPS*GS_BATCH,
+// its lanes side by side along the row (four neighbouring elements each: dim <= 128, vd <= 128 * GS_VPASS).
+// The rows of a batch of keys and values are asked for before the first is used.  Every warp runs its own
+// softmax (maximum, sum and weighted value sum per head, the same in all its lanes); the warps' parts meet in
+// shared memory in warp order, where the extra term joins, and a thread per (head, value dimension) scales,
+// gates and stores.  What a warp adds up depends on the key's number only, so a token's result is the same
+// whatever else the step holds.
+#define GS_THREADS 256
+#define GS_WARPS (GS_THREADS / 32)
+#define GS_BATCH 4
+#define GS_VPASS 2
+
+template <int REP>
+__global__ void __launch_bounds__(GS_THREADS)
+gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, DiffCache cache,
+                            bf16* __restrict__ out, const int* __restrict__ items, const int* __restrict__ positions,
+                            const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                            const int* __restrict__ block_table, int nh, float scale, GqaMask mask, int has_sink,
+                            float sink, GqaEpilogue epi, int* __restrict__ status) {
+    extern __shared__ __align__(16) float gs_smem[];      // [GS_WARPS][REP][vd + 2]: weighted sums, maximum, sum
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int t = items ? items[blockIdx.x] : blockIdx.x, kvh = blockIdx.y;
+    if (t < 0) return;
+    const int pos = positions[t];
+    if (pos < 0) return;
+    const int nkv = cache.nkv, vd = cache.vd, dim = cache.kd, ps = cache.page_size;
+    const int rep = nh / nkv, h0 = kvh * rep;
+    const int* bt = block_table + (size_t)slots[seq_of_token[t]] * cache.max_pages;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lo = gqa_lo(pos, mask), head_end = gqa_head_end(lo, mask);
+    const int total = head_end + pos + 1 - lo;
+    const int e_k = 4 * lane;
+    float qr[REP][4];
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rep && e_k < dim) v = load4_cg(q + ((size_t)t * nh + h0 + r) * dim + e_k);
+        qr[r][0] = v.x * scale; qr[r][1] = v.y * scale; qr[r][2] = v.z * scale; qr[r][3] = v.w * scale;
+    }
+    float acc[REP][GS_VPASS][4], m[REP], l[REP];
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+        m[r] = -INFINITY;
+        l[r] = 0.f;
+#pragma unroll
+        for (int p = 0; p < GS_VPASS; ++p)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[r][p][x] = 0.f;
+    }
+    for (int i0 = warp * GS_BATCH; i0 < total; i0 += GS_WARPS * GS_BATCH) {
+        float4 kk[GS_BATCH], vv[GS_BATCH][GS_VPASS];
+        bool seen[GS_BATCH];
+#pragma unroll
+        for (int u = 0; u < GS_BATCH; ++u) {
+            const int i = i0 + u;
+            const int key = i < head_end ? i : lo + (i - head_end);
+            int page = -1;
+            if (i < total) {
+                page = bt[key / ps];
+                if (page < 0 && status) *status = 1;
+            }
+            seen[u] = page >= 0;
+            kk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int p = 0; p < GS_VPASS; ++p) vv[u][p] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (page >= 0) {
+                if (e_k < dim) kk[u] = load4_cg(cache_keys(pool, cache, page, kvh, key % ps) + e_k);
+                const bf16* vrow = cache_values(pool, cache, page, kvh, key % ps);
+#pragma unroll
+                for (int p = 0; p < GS_VPASS; ++p)
+                    if (p * 128 + e_k < vd) vv[u][p] = load4_cg(vrow + p * 128 + e_k);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < GS_BATCH; ++u) {
+            if (!seen[u]) continue;                        // (the same in all lanes of the warp)
+#pragma unroll
+            for (int r = 0; r < REP; ++r) {
+                if (r >= rep) continue;
+                float s = fmaf(qr[r][0], kk[u].x, fmaf(qr[r][1], kk[u].y, fmaf(qr[r][2], kk[u].z, qr[r][3] * kk[u].w)));
+                s = warp_sum(s);
+                const float n = fmaxf(m[r], s);
+                const float c = m[r] == -INFINITY ? 0.f : expf(m[r] - n);
+                const float w = expf(s - n);
+                l[r] = fmaf(l[r], c, w);
+                m[r] = n;
+#pragma unroll
+                for (int p = 0; p < GS_VPASS; ++p) {
+                    acc[r][p][0] = fmaf(w, vv[u][p].x, acc[r][p][0] * c);
+                    acc[r][p][1] = fmaf(w, vv[u][p].y, acc[r][p][1] * c);
+                    acc[r][p][2] = fmaf(w, vv[u][p].z, acc[r][p][2] * c);
+                    acc[r][p][3] = fmaf(w, vv[u][p].w, acc[r][p][3] * c);
+                }
+            }
+        }
+    }
+    const int ld = vd + 2;
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+        if (r >= rep) continue;
+        float* dst = gs_smem + ((size_t)warp * REP + r) * ld;
+#pragma unroll
+        for (int p = 0; p < GS_VPASS; ++p)
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+                if (p * 128 + e_k + x < vd) dst[p * 128 + e_k + x] = acc[r][p][x];
+        if (lane == 0) { dst[vd] = m[r]; dst[vd + 1] = l[r]; }
+    }
+    __syncthreads();
+    const bf16* gate = reinterpret_cast<const bf16*>(epi.gate);
+    for (int idx = threadIdx.x; idx < rep * vd; idx += GS_THREADS) {
+        const int r = idx / vd, e = idx % vd;
+        float M = has_sink ? sink : -INFINITY;
+        for (int w = 0; w < GS_WARPS; ++w) M = fmaxf(M, gs_smem[((size_t)w * REP + r) * ld + vd]);
+        float L = has_sink ? expf(sink - M) : 0.f, O = 0.f;
+        for (int w = 0; w < GS_WARPS; ++w) {
+            const float* src = gs_smem + ((size_t)w * REP + r) * ld;
+            const float mw = src[vd];
+            if (mw == -INFINITY) continue;
+            const float c = expf(mw - M);
+            L = fmaf(src[vd + 1], c, L);
+            O = fmaf(src[e], c, O);
+        }
+        float o = L > 0.f ? O * epi.out_scale / L : 0.f;
+        const int h = h0 + r;
+        if (gate) o *= sigmoidf_(load1_cg(gate + (size_t)t * epi.gate_ld + h * vd + e));
+        out[((size_t)t * nh + h) * vd + e] = __float2bfloat16_rn(o);
+    }
+}
+
+ST_EXPORT int st_gqa_attention_single_applies(int nh, int nkv, int dim, int vd) {
+    return nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 8 && dim > 0 && vd > 0 && dim % 4 == 0 && vd % 4 == 0 &&
+           dim <= 128 && vd <= 128 * GS_VPASS;
+}
+
+template <int REP>
+static int launch_gqa_single(const void* q, const void* pool, const DiffCache& c, void* out, const int* items,
+                             const int* positions, const int* seq_of_token, const int* slots, const int* block_table,
+                             int n_tokens, int nh, float scale, const GqaMask& mask, int has_sink, float sink,
+                             const GqaEpilogue& epi, int* status, cudaStream_t s) {
+    const size_t smem = (size_t)GS_WARPS * REP * (c.vd + 2) * sizeof(float);
+    auto kern = gqa_attention_single_kernel<REP>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return st_launch_pdl("gqa_single", kern, dim3(n_tokens, c.nkv), dim3(GS_THREADS), smem, s, (const bf16*)q,
+                         (const bf16*)pool, c, (bf16*)out, items, positions, seq_of_token, slots, block_table, nh, scale,
+                         mask, has_sink, sink, epi, status);
+}
+
+// bfloat16 only; `items` as for the plain kernel
+ST_EXPORT int st_gqa_attention_single(const void* q, const void* pool, long long page_stride, long long entry_offset,
+                                      void* out, const int* items, const int* positions, const int* seq_of_token,
+                                      const int* slots, const int* block_table, int max_pages, int n_tokens, int nh,
+                                      int nkv, int dim, int vd, int page_size, float scale, int window, int keep_first,
+                                      int has_sink, float sink, const void* gate, long long gate_ld, float out_scale,
+                                      int* status, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (page_size <= 0 || keep_first < 0) return ST_ERR_BAD_ARG;
+    if (!st_gqa_attention_single_applies(nh, nkv, dim, vd)) return ST_ERR_BAD_SIZE;
+    const DiffCache c = {max_pages, page_size, nkv, dim, vd, page_stride, entry_offset};
+    const GqaMask mask = {window, keep_first};
+    const GqaEpilogue epi = {gate, gate_ld, out_scale};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int rep = nh / nkv;
+#define GS_ARGS q, pool, c, out, items, positions, seq_of_token, slots, block_table, n_tokens, nh, scale, mask, has_sink, sink, \
+                epi, status, s
+    if (rep == 1) return launch_gqa_single<1>(GS_ARGS);
+    if (rep == 2) return launch_gqa_single<2>(GS_ARGS);
+    if (rep <= 4) return launch_gqa_single<4>(GS_ARGS);
+    return launch_gqa_single<8>(GS_ARGS);
+#undef GS_ARGS
+}

@@ -1220,7 +1220,53 @@ def gated_clamped_act(gu: torch.Tensor, bias: Optional[torch.Tensor], limit: flo
     return out
 
 
-def gqa_attention_fast_applies(q: torch.Tensor, dim: int, vd: int) -> bool:
-    """Whether the bfloat16 kernels (query tiles on the tensor cores, single tokens with 16-byte accesses) take
-    these sizes."""
-    return False
+def gqa_attention_fast_applies(q: torch.Tensor, nh: int, nkv: int, dim: int, vd: int) -> bool:
+    """Whether the bfloat16 kernels (query tiles on the tensor cores; single tokens a block per key/value head with
+    8-byte accesses) take these sizes: dim and vd multiples of 8, dim <= 128, vd <= 256, at most eight query heads
+    per key/value head."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and bool(lib().st_gqa_attention_tiles_applies(dim, vd))
+            and bool(lib().st_gqa_attention_single_applies(nh, nkv, dim, vd)))
+
+
+def gqa_attention_tiles(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, tiles: torch.Tensor,
+                        n_tiles: int, tile_rows: int, q_start: torch.Tensor, start_pos: torch.Tensor,
+                        slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, dim: int, vd: int,
+                        page_size: int, scale: float, window: int, keep_first: int, sink: Optional[float],
+                        gate: Optional[torch.Tensor], gate_off: int, out_scale: float,
+                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same attention for tiles of ``tile_rows`` query rows (tiles: int32 [n_tiles, 2] = request of the step,
+    offset of the tile among its new tokens) on the warp-level tensor cores, bfloat16 only."""
+    if not (q.dtype == torch.bfloat16 and bool(lib().st_gqa_attention_tiles_applies(dim, vd))):
+        raise KernelError("gqa_attention_tiles: bfloat16, dim and vd multiples of 8, dim <= 128, vd <= 256")
+    assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
+    stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink,
+                                               gate, gate_off, out_scale)
+    _check(lib().st_gqa_attention_tiles(_p(q), _p(pool), stride, off, _p(out), _p(tiles), n_tiles, tile_rows,
+                                        _p(q_start), _p(start_pos), _p(slots), _p(block_table), block_table.shape[1],
+                                        nh, nkv, dim, vd, page_size, _f(scale), window, keep_first,
+                                        int(sink is not None), _f(sink or 0.0), gate_ptr, gate_ld, _f(out_scale),
+                                        _p(status), _stream()), "gqa_attention_tiles")
+    return out
+
+
+def gqa_attention_single(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
+                         seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int,
+                         dim: int, vd: int, page_size: int, scale: float, window: int, keep_first: int,
+                         sink: Optional[float], gate: Optional[torch.Tensor], gate_off: int, out_scale: float,
+                         status: Optional[torch.Tensor] = None, items: Optional[torch.Tensor] = None,
+                         n_items: Optional[int] = None) -> torch.Tensor:
+    """The same attention token by token in bfloat16, one block per (token, key/value head) for all the query heads
+    that read it; ``items`` as for the plain kernel."""
+    if not (q.dtype == torch.bfloat16 and bool(lib().st_gqa_attention_single_applies(nh, nkv, dim, vd))):
+        raise KernelError("gqa_attention_single: bfloat16, dim and vd multiples of 4, dim <= 128, vd <= 256, at most "
+                          "eight query heads per key/value head")
+    assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
+    stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink,
+                                               gate, gate_off, out_scale)
+    n = q.shape[0] if items is None else (n_items if n_items is not None else items.numel())
+    _check(lib().st_gqa_attention_single(_p(q), _p(pool), stride, off, _p(out), _p(items), _p(positions),
+                                         _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1], n, nh, nkv,
+                                         dim, vd, page_size, _f(scale), window, keep_first, int(sink is not None),
+                                         _f(sink or 0.0), gate_ptr, gate_ld, _f(out_scale), _p(status), _stream()),
+           "gqa_attention_single")
+    return out

@@ -129,7 +129,7 @@ class GroupedAttention(Mixer):
         gate, gate_off = (proj, self.qw + self.kw + self.vw) if self.gate else (None, 0)
         consts = (self.nh, self.nkv, self.dim, self.vdim, ps, self.scale, self.window or 0, self.keep_first, self.sink,
                   gate, gate_off, self.out_scale)
-        if ops.gqa_attention_fast_applies(q, self.dim, self.vdim):
+        if ops.gqa_attention_fast_applies(q, self.nh, self.nkv, self.dim, self.vdim):
             plan = ctx.plan(PagedAttentionPlan.name)
             if plan.n_tiles:
                 ops.gqa_attention_tiles(q, cache.pool, cache.layer, o, plan.tiles, plan.n_tiles, self._plan.tile_rows,

@@ -227,11 +227,16 @@ def gated_attention(h, w, p, mx, kv):
     return o @ w[p + "o"].T + w[p + "o.b"]
 
 
+def clamped_unit(a, b, limit):
+    """g = min(a, limit), u = clamp(b, -limit, limit): g * sigmoid(1.702 g) * (u + 1)."""
+    g = np.minimum(a, limit)
+    u = np.clip(b, -limit, limit)
+    return g * sigmoid(1.702 * g) * (u + 1.0)
+
+
 def feed_forward(h, w, p, mlp):
-    L = mlp["limit"]
-    g = np.minimum(h @ w[p + "gate"].T + w[p + "gate.b"], L)
-    u = np.clip(h @ w[p + "up"].T + w[p + "up.b"], -L, L)
-    return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T + w[p + "down.b"]
+    y = clamped_unit(h @ w[p + "gate"].T + w[p + "gate.b"], h @ w[p + "up"].T + w[p + "up.b"], mlp["limit"])
+    return y @ w[p + "down"].T + w[p + "down.b"]
 
 
 def forward(cfg, w, tokens, return_layers=False):
