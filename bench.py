@@ -13,9 +13,9 @@ single-GPU and exits with 2.
 ``--only decode|prefill`` run one small measurement (for profiling); ``--only mixed`` runs a continuous
 batch of requests of random lengths (prompt portions of 512 tokens beside decoded tokens) through
 ``LLMEngine.generate`` and reports tokens per second, steps and preemptions.  ``--only designs`` measures a
-Fanidra model and a Pikadra model beside an OPT model of equal width, depth and parameter count (prefill, decode, and
-the device time of every operation of one step of each kind; ``--model-name w2048|w4096`` picks one size, ``--layers``
-the depth, ``--designs`` which of the three).
+Fanidra, a Pikadra and a Norelix model beside an OPT model of equal width, depth and parameter count (prefill, decode,
+and the device time of every operation of one step of each kind; ``--model-name w2048|w4096`` picks one size,
+``--layers`` the depth, ``--designs`` which of the four).
 """
 import argparse
 import json
@@ -104,6 +104,10 @@ def prefill_flops(cfg, n_layers, n):
 # The Pikadra model of a size: latent attention (key/value latent of 512 + 64 rotated numbers per token), layers with
 # a dense gated feed-forward alternating with mixtures (8 experts, 2 per token, plus a shared expert); parameter bytes
 # per layer within 7 % of OPT's.
+# The Norelix model of a size: layers that pair a windowed grouped attention (the Fanidra attention's head sizes and
+# window, four kept first keys) with a gated delta rule (half the recurrence's heads, on half as many query/key heads),
+# alternating with gated grouped attention over all keys; every second of those reads the keys and values of the one
+# before.  With the same feed-forward size its parameter count is within 1 % of the Fanidra model's.
 DESIGN_SIZES = {
     "w2048": dict(width=2048, opt_heads=32, opt_ffn=8192, heads=16, kv_heads=4, dim=64, vdim=128, ff=5504,
                   rec_heads=16, rec_dim=128, rec_vdim=128, block=512,
@@ -124,7 +128,7 @@ def compare_designs(args, peaks):
     import numpy as np
     import torch
     from swifttransformer_b200 import ops
-    from swifttransformer_b200.config import FanidraConfig, OptConfig, PikadraConfig
+    from swifttransformer_b200.config import FanidraConfig, NorelixConfig, OptConfig, PikadraConfig
     from swifttransformer_b200.engine.engine import LLMEngine
     from swifttransformer_b200.engine.step import StepEntry
     from swifttransformer_b200.models import random_model
@@ -158,7 +162,19 @@ def compare_designs(args, peaks):
         pik = PikadraConfig.from_dict(dict(architecture="Pikadra", vocab=vocab, width=z["width"], norm={"eps": 1e-5},
                                            embedding={"scale": 8.0}, logit_scale=0.5, logit_softcap=20.0,
                                            layers=[routed if i % 2 else dense for i in range(n_layers)]))
-        all_designs = {"fanidra": fan, "pikadra": pik, "opt": opt}
+        nx_mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+        nx_left = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5,
+                       mask={"size": z["block"], "keep_first": 4}, rot={"dims": z["dim"], "base": 10000.0})
+        nx_right = dict(heads=z["rec_heads"] // 2, kv_heads=z["rec_heads"] // 4, dim=z["rec_dim"], vdim=z["rec_vdim"], conv=4)
+        nx_att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5,
+                      q_temp={"coef": 0.1, "every": 512})
+        nx_layers = [{"type": "parallel", "mlp": nx_mlp,
+                      "mixer": {"left": nx_left, "right": nx_right, "left_scale": 1.0, "right_scale": 1.0}} if i % 2 == 0 else
+                     {"type": "attention", "mlp": nx_mlp, "mixer": dict(nx_att, kv_from=i - 2) if i % 4 == 3 else nx_att}
+                     for i in range(n_layers)]
+        nor = NorelixConfig.from_dict(dict(architecture="Norelix", vocab=vocab, width=z["width"], norm={"eps": 1e-5},
+                                           layers=nx_layers))
+        all_designs = {"fanidra": fan, "pikadra": pik, "norelix": nor, "opt": opt}
         return {d: c for d, c in all_designs.items() if not args.designs or d in args.designs.split(",")}
 
     def engine(model, graphs=True):
@@ -261,7 +277,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (0: all)")
     ap.add_argument("--designs", default="", help="with --only designs: which designs to measure, with commas between "
-                    "them (fanidra, pikadra, opt; default: all)")
+                    "them (fanidra, pikadra, norelix, opt; default: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-big", action="store_true", help="skip the OPT-6.7B and OPT-30B points (13 and 60 GB of random weights)")
     ap.add_argument("--launch-floor", action="store_true",
