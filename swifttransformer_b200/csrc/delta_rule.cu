@@ -13,7 +13,7 @@
 // Three kernels.  delta_prepare turns a token's row of the float projection [q | k | v | b | a1 | g1] into a
 // float row [q (G*dim) | k (G*dim) | v (H*vd) | decay (H*dim) | beta (H)]; delta_scan walks each request's
 // tokens with the state's columns in registers (a column of S evolves on its own: its dot products with k and q
-// are sums over dim, shared by the L lanes that hold the column); delta_output norms and gates each head's o.
+// are sums over dim, shared by the L lanes that hold the column) and the tokens' rows staged in shared memory; delta_output norms and gates each head's o.
 // Everything here is float arithmetic; only the low-rank matrices and the result are in the storage type.
 //
 // Since (decay S + k u^T)^T q = (decay S)^T q + u (k . q), both dot products of a token are taken from the
@@ -121,14 +121,41 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, DeltaShape sh, cons
 
 // ------------------------------------------------------------------------------------------------
 // The recurrence.  grid (requests of the step, H, column groups); a block of DS_THREADS threads holds
-// DS_THREADS / L columns of one head's state, L lanes per column with R consecutive rows each (dim <= L * R).
+// DS_THREADS / L columns of one head's state, L lanes per column with R rows each (dim <= L * R); lane `sub` of a
+// column holds rows sub * R .. sub * R + R - 1.
+//
+// A token's step is short (a few hundred cycles) and the next one cannot start before it ends, so a trip to
+// memory per token would be most of the time.  The block therefore brings the prepared rows of DS_CHUNK tokens at
+// a time into shared memory with asynchronous 4-byte copies, DS_STAGES chunks deep: per token the head's k, q and
+// decays (dimension sub * R + r at r * L + sub, so that the lanes of a column read neighbouring banks and the
+// columns of a warp the same word), the block's values and beta.  Every thread then reads its 3 R numbers of the
+// next token from shared memory while this token's sums travel through the shuffles.
 #define DS_THREADS 128
+#define DS_CHUNK 8
+#define DS_STAGES 3
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void ds_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void ds_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+template <int L, int R>
+struct DeltaScanSmem {
+    static constexpr int COLS = DS_THREADS / L;
+    static constexpr int DP = L * R;                     // padded key size
+    static constexpr int ROW = 3 * DP + COLS + 1;        // k | q | decay | the block's values | beta
+    static constexpr size_t BYTES = (size_t)DS_STAGES * DS_CHUNK * ROW * sizeof(float);
+};
 
 template <int L, int R>
 __global__ void __launch_bounds__(DS_THREADS)
 delta_scan_kernel(const float* __restrict__ prep, DeltaShape sh, float* __restrict__ state, int write_state,
                   float* __restrict__ o_out, const int* __restrict__ positions, const int* __restrict__ q_start,
                   const int* __restrict__ slots) {
+    using M = DeltaScanSmem<L, R>;
+    extern __shared__ __align__(16) float ds_smem[];
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
     const int b = blockIdx.x, h = blockIdx.y;
@@ -137,7 +164,8 @@ delta_scan_kernel(const float* __restrict__ prep, DeltaShape sh, float* __restri
     const int H = sh.H, dim = sh.dim, vd = sh.vd;
     const int g = h / (H / sh.G);
     const int sub = threadIdx.x % L;
-    const int col = blockIdx.z * (DS_THREADS / L) + threadIdx.x / L;
+    const int col0 = blockIdx.z * M::COLS;
+    const int col = col0 + threadIdx.x / L;
     const bool live = col < vd;
     const int d0 = sub * R;
     float* S = state + (((size_t)slots[b] * H + h) * dim) * vd + col;
@@ -146,44 +174,83 @@ delta_scan_kernel(const float* __restrict__ prep, DeltaShape sh, float* __restri
     for (int r = 0; r < R; ++r) s[r] = (live && d0 + r < dim) ? S[(size_t)(d0 + r) * vd] : 0.f;
     const int row_len = sh.row();
     const float* p = prep + (size_t)first * row_len;
+    // the padding of the staged rows (dimensions past dim, columns past vd) stays zero: nothing is copied there
+    for (int i = threadIdx.x; i < DS_STAGES * DS_CHUNK * M::ROW; i += DS_THREADS) ds_smem[i] = 0.f;
+    __syncthreads();
+    const int n_chunks = (n + DS_CHUNK - 1) / DS_CHUNK;
+    auto stage_chunk = [&](int c) {
+        float* dst0 = ds_smem + (size_t)(c % DS_STAGES) * DS_CHUNK * M::ROW;
+        const int t_end = min(DS_CHUNK, n - c * DS_CHUNK);
+        for (int t = 0; t < t_end; ++t) {
+            const float* row = p + (size_t)(c * DS_CHUNK + t) * row_len;
+            float* dst = dst0 + t * M::ROW;
+            for (int j = threadIdx.x; j < dim; j += DS_THREADS) {
+                const int at = (j % R) * L + j / R;
+                cp_async4(dst + at, row + sh.pk() + g * dim + j);
+                cp_async4(dst + M::DP + at, row + sh.pq() + g * dim + j);
+                cp_async4(dst + 2 * M::DP + at, row + sh.pd() + h * dim + j);
+            }
+            if (threadIdx.x < M::COLS) {
+                if (col0 + threadIdx.x < vd) cp_async4(dst + 3 * M::DP + threadIdx.x, row + sh.pv() + h * vd + col0 + threadIdx.x);
+            } else if (threadIdx.x == M::COLS) {
+                cp_async4(dst + 3 * M::DP + M::COLS, row + sh.pb() + h);
+            }
+        }
+    };
+#pragma unroll
+    for (int c = 0; c < DS_STAGES - 1; ++c) {
+        if (c < n_chunks) stage_chunk(c);
+        ds_commit();
+    }
     float kq[R], qq[R], dd[R], v, beta;
     auto fetch = [&](const float* row) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            const bool in = d0 + r < dim;
-            kq[r] = in ? __ldcg(row + sh.pk() + g * dim + d0 + r) : 0.f;
-            qq[r] = in ? __ldcg(row + sh.pq() + g * dim + d0 + r) : 0.f;
-            dd[r] = in ? __ldcg(row + sh.pd() + h * dim + d0 + r) : 0.f;
+            kq[r] = row[r * L + sub];
+            qq[r] = row[M::DP + r * L + sub];
+            dd[r] = row[2 * M::DP + r * L + sub];
         }
-        v = live ? __ldcg(row + sh.pv() + h * vd + col) : 0.f;
-        beta = __ldcg(row + sh.pb() + h);
+        v = row[3 * M::DP + threadIdx.x / L];
+        beta = row[3 * M::DP + M::COLS];
     };
-    fetch(p);
-    for (int t = 0; t < n; ++t) {
-        float k_[R], q_[R];
-        float sk = 0.f, sq = 0.f, kdq = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+        ds_wait<DS_STAGES - 2>();           // chunk c has landed (this thread's copies; the barrier makes it all threads')
+        __syncthreads();                    // also: every thread is done with chunk c - 1, whose stage is filled next
+        if (c + DS_STAGES - 1 < n_chunks) stage_chunk(c + DS_STAGES - 1);
+        ds_commit();
+        const float* rows = ds_smem + (size_t)(c % DS_STAGES) * DS_CHUNK * M::ROW;
+        const int t_end = min(DS_CHUNK, n - c * DS_CHUNK);
+        fetch(rows);
+        for (int t = 0; t < t_end; ++t) {
+            float k_[R];
+            // partial sums in four lanes of arithmetic, so that the chain of additions is R / 4 long
+            float sk4[4] = {0.f, 0.f, 0.f, 0.f}, sq4[4] = {0.f, 0.f, 0.f, 0.f}, kq4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            k_[r] = kq[r];
-            q_[r] = qq[r];
-            s[r] *= dd[r];
-            sk = fmaf(s[r], k_[r], sk);
-            sq = fmaf(s[r], q_[r], sq);
-            kdq = fmaf(k_[r], q_[r], kdq);
+            for (int r = 0; r < R; ++r) {
+                k_[r] = kq[r];
+                s[r] *= dd[r];
+                sk4[r & 3] = fmaf(s[r], k_[r], sk4[r & 3]);
+                sq4[r & 3] = fmaf(s[r], qq[r], sq4[r & 3]);
+                kq4[r & 3] = fmaf(k_[r], qq[r], kq4[r & 3]);
+            }
+            float sk = (sk4[0] + sk4[1]) + (sk4[2] + sk4[3]);
+            float sq = (sq4[0] + sq4[1]) + (sq4[2] + sq4[3]);
+            float kdq = (kq4[0] + kq4[1]) + (kq4[2] + kq4[3]);
+            const float v_now = v, beta_now = beta;
+            if (t + 1 < t_end) fetch(rows + (t + 1) * M::ROW);      // the next token's numbers are on their way meanwhile
+#pragma unroll
+            for (int o = L / 2; o > 0; o >>= 1) {
+                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                kdq += __shfl_xor_sync(0xffffffffu, kdq, o);
+            }
+            const float u = beta_now * (v_now - sk);
+#pragma unroll
+            for (int r = 0; r < R; ++r) s[r] = fmaf(k_[r], u, s[r]);
+            if (live && sub == 0) o_out[(size_t)(first + c * DS_CHUNK + t) * H * vd + h * vd + col] = fmaf(u, kdq, sq);
         }
-        const float v_now = v, beta_now = beta;
-        if (t + 1 < n) fetch(p + (size_t)(t + 1) * row_len);      // the next token's row is on its way meanwhile
-#pragma unroll
-        for (int o = L / 2; o > 0; o >>= 1) {
-            sk += __shfl_xor_sync(0xffffffffu, sk, o);
-            sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            kdq += __shfl_xor_sync(0xffffffffu, kdq, o);
-        }
-        const float u = beta_now * (v_now - sk);
-#pragma unroll
-        for (int r = 0; r < R; ++r) s[r] = fmaf(k_[r], u, s[r]);
-        if (live && sub == 0) o_out[(size_t)(first + t) * H * vd + h * vd + col] = fmaf(u, kdq, sq);
     }
+    ds_wait<0>();
     if (write_state && live) {
 #pragma unroll
         for (int r = 0; r < R; ++r)
@@ -264,8 +331,17 @@ ST_EXPORT int st_delta_rule(const float* proj, int ld, int q_off, int b_off, int
     }
     {
 #define DS_LAUNCH(L, R)                                                                                              \
-    rc = st_launch_pdl("delta_scan", delta_scan_kernel<L, R>, dim3(n_seqs, H, (vd + DS_THREADS / L - 1) / (DS_THREADS / L)), \
-                       dim3(DS_THREADS), 0, s, (const float*)prep, sh, state, write_state, o, positions, q_start, slots)
+    do {                                                                                                             \
+        const size_t smem = DeltaScanSmem<L, R>::BYTES;                                                              \
+        if (smem > 48 * 1024) {                                                                                      \
+            cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<L, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 (int)smem);                                                         \
+            if (e != cudaSuccess) return (int)e;                                                                     \
+        }                                                                                                            \
+        rc = st_launch_pdl("delta_scan", delta_scan_kernel<L, R>,                                                    \
+                           dim3(n_seqs, H, (vd + DS_THREADS / L - 1) / (DS_THREADS / L)), dim3(DS_THREADS), smem, s, \
+                           (const float*)prep, sh, state, write_state, o, positions, q_start, slots);                \
+    } while (0)
         if (dim <= 32) DS_LAUNCH(8, 4);
         else if (dim <= 64) DS_LAUNCH(8, 8);
         else if (dim <= 128) DS_LAUNCH(8, 16);

@@ -217,17 +217,21 @@ ST_EXPORT int st_gqa_attention_plain(const void* q, const void* pool, long long 
 // ------------------------------------------------------------------------------------------------
 // Single tokens and short portions in bfloat16: one block per (token, key/value head) serves all REP query heads
 // of the group, so a key or value row is fetched once for them.  The seen keys (the kept first ones, then the
-// window up to the query) are numbered in one run; warp w takes keys w*GS_BATCH .. of every GS_WARPS*GS_BATCH,
-// its lanes side by side along the row (four neighbouring elements each: dim <= 128, vd <= 128 * GS_VPASS).
-// The rows of a batch of keys and values are asked for before the first is used.  Every warp runs its own
-// softmax (maximum, sum and weighted value sum per head, the same in all its lanes); the warps' parts meet in
-// shared memory in warp order, where the extra term joins, and a thread per (head, value dimension) scales,
-// gates and stores.  What a warp adds up depends on the key's number only, so a token's result is the same
-// whatever else the step holds.
+// window up to the query) are numbered in one run and taken GS_TILE at a time, in two phases:
+//   scores   a thread per key: it looks the key's page up, asks for the whole key row in 16-byte pieces at once
+//            (GS_TILE rows are on their way together) and takes the dot products with the group's queries, which
+//            stand in shared memory as scaled floats; the tile's maximum per head is found over the block, and the
+//            weights exp(s - m) go to shared memory with the address of the key's value row;
+//   values   warp w takes keys w, w + GS_WARPS, .. of the tile, its lanes side by side along the value row (four
+//            neighbouring elements each: vd <= 128 * GS_VPASS), several rows in flight.
+// The running maximum is the block's, so the warps' sums only have to be added at the end, where the extra term
+// joins and a thread per (head, value dimension) scales, gates and stores.  What is added in which order depends
+// on the key's number only, so a token's result is the same whatever else the step holds.
 #define GS_THREADS 256
 #define GS_WARPS (GS_THREADS / 32)
-#define GS_BATCH 4
+#define GS_TILE GS_THREADS
 #define GS_VPASS 2
+#define GS_KPIECES 8      // 16-byte pieces of a key row asked for at once (64 dimensions)
 
 template <int REP>
 __global__ void __launch_bounds__(GS_THREADS)
@@ -236,7 +240,7 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             const int* __restrict__ seq_of_token, const int* __restrict__ slots,
                             const int* __restrict__ block_table, int nh, float scale, GqaMask mask, int has_sink,
                             float sink, GqaEpilogue epi, int* __restrict__ status) {
-    extern __shared__ __align__(16) float gs_smem[];      // [GS_WARPS][REP][vd + 2]: weighted sums, maximum, sum
+    extern __shared__ __align__(16) unsigned char gs_raw[];
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
     const int t = items ? items[blockIdx.x] : blockIdx.x, kvh = blockIdx.y;
@@ -245,18 +249,21 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     if (pos < 0) return;
     const int nkv = cache.nkv, vd = cache.vd, dim = cache.kd, ps = cache.page_size;
     const int rep = nh / nkv, h0 = kvh * rep;
+    long long* srow = reinterpret_cast<long long*>(gs_raw);             // [GS_TILE] value rows (element offsets), -1: none
+    float* sq = reinterpret_cast<float*>(srow + GS_TILE);               // [REP][dim] queries times scale
+    float* sp = sq + REP * dim;                                         // [REP][GS_TILE] weights
+    float* sred = sp + REP * GS_TILE;                                   // [REP][GS_WARPS]
+    float* sl = sred + REP * GS_WARPS;                                  // [GS_WARPS][REP] sums of weights
+    float* so = sl + GS_WARPS * REP;                                    // [GS_WARPS][REP][vd] weighted value sums
     const int* bt = block_table + (size_t)slots[seq_of_token[t]] * cache.max_pages;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lo = gqa_lo(pos, mask), head_end = gqa_head_end(lo, mask);
     const int total = head_end + pos + 1 - lo;
-    const int e_k = 4 * lane;
-    float qr[REP][4];
-#pragma unroll
-    for (int r = 0; r < REP; ++r) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < rep && e_k < dim) v = load4_cg(q + ((size_t)t * nh + h0 + r) * dim + e_k);
-        qr[r][0] = v.x * scale; qr[r][1] = v.y * scale; qr[r][2] = v.z * scale; qr[r][3] = v.w * scale;
+    for (int i = threadIdx.x; i < REP * dim; i += GS_THREADS) {
+        const int r = i / dim;
+        sq[i] = r < rep ? load1_cg(q + ((size_t)t * nh + h0) * dim + i) * scale : 0.f;
     }
+    const int e_v = 4 * lane;
     float acc[REP][GS_VPASS][4], m[REP], l[REP];
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
@@ -267,79 +274,130 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 #pragma unroll
             for (int x = 0; x < 4; ++x) acc[r][p][x] = 0.f;
     }
-    for (int i0 = warp * GS_BATCH; i0 < total; i0 += GS_WARPS * GS_BATCH) {
-        float4 kk[GS_BATCH], vv[GS_BATCH][GS_VPASS];
-        bool seen[GS_BATCH];
-#pragma unroll
-        for (int u = 0; u < GS_BATCH; ++u) {
-            const int i = i0 + u;
-            const int key = i < head_end ? i : lo + (i - head_end);
-            int page = -1;
-            if (i < total) {
-                page = bt[key / ps];
-                if (page < 0 && status) *status = 1;
-            }
-            seen[u] = page >= 0;
-            kk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int p = 0; p < GS_VPASS; ++p) vv[u][p] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (page >= 0) {
-                if (e_k < dim) kk[u] = load4_cg(cache_keys(pool, cache, page, kvh, key % ps) + e_k);
-                const bf16* vrow = cache_values(pool, cache, page, kvh, key % ps);
-#pragma unroll
-                for (int p = 0; p < GS_VPASS; ++p)
-                    if (p * 128 + e_k < vd) vv[u][p] = load4_cg(vrow + p * 128 + e_k);
-            }
+    __syncthreads();
+    const int pieces = dim / 8;
+    for (int i0 = 0; i0 < total; i0 += GS_TILE) {
+        // ---- scores: this thread's key
+        const int i = i0 + threadIdx.x;
+        const int key = i < head_end ? i : lo + (i - head_end);
+        int page = -1;
+        if (i < total) {
+            page = bt[key / ps];
+            if (page < 0 && status) *status = 1;
         }
+        float s[REP];
 #pragma unroll
-        for (int u = 0; u < GS_BATCH; ++u) {
-            if (!seen[u]) continue;                        // (the same in all lanes of the warp)
+        for (int r = 0; r < REP; ++r) s[r] = 0.f;
+        if (page >= 0) {
+            const uint4* kp = reinterpret_cast<const uint4*>(cache_keys(pool, cache, page, kvh, key % ps));
+            for (int c0 = 0; c0 < pieces; c0 += GS_KPIECES) {
+                uint4 kk[GS_KPIECES];
 #pragma unroll
-            for (int r = 0; r < REP; ++r) {
-                if (r >= rep) continue;
-                float s = fmaf(qr[r][0], kk[u].x, fmaf(qr[r][1], kk[u].y, fmaf(qr[r][2], kk[u].z, qr[r][3] * kk[u].w)));
-                s = warp_sum(s);
-                const float n = fmaxf(m[r], s);
-                const float c = m[r] == -INFINITY ? 0.f : expf(m[r] - n);
-                const float w = expf(s - n);
-                l[r] = fmaf(l[r], c, w);
-                m[r] = n;
+                for (int c = 0; c < GS_KPIECES; ++c)
+                    kk[c] = c0 + c < pieces ? __ldcg(kp + c0 + c) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-                for (int p = 0; p < GS_VPASS; ++p) {
-                    acc[r][p][0] = fmaf(w, vv[u][p].x, acc[r][p][0] * c);
-                    acc[r][p][1] = fmaf(w, vv[u][p].y, acc[r][p][1] * c);
-                    acc[r][p][2] = fmaf(w, vv[u][p].z, acc[r][p][2] * c);
-                    acc[r][p][3] = fmaf(w, vv[u][p].w, acc[r][p][3] * c);
+                for (int c = 0; c < GS_KPIECES; ++c) {
+                    if (c0 + c >= pieces) continue;
+                    const uint32_t w4[4] = {kk[c].x, kk[c].y, kk[c].z, kk[c].w};
+                    float kf[8];
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        kf[2 * x] = __uint_as_float(w4[x] << 16);
+                        kf[2 * x + 1] = __uint_as_float(w4[x] & 0xffff0000u);
+                    }
+#pragma unroll
+                    for (int r = 0; r < REP; ++r) {
+                        const float4 qa = *reinterpret_cast<const float4*>(sq + r * dim + (c0 + c) * 8);
+                        const float4 qb = *reinterpret_cast<const float4*>(sq + r * dim + (c0 + c) * 8 + 4);
+                        float d = s[r];
+                        d = fmaf(qa.x, kf[0], d); d = fmaf(qa.y, kf[1], d); d = fmaf(qa.z, kf[2], d); d = fmaf(qa.w, kf[3], d);
+                        d = fmaf(qb.x, kf[4], d); d = fmaf(qb.y, kf[5], d); d = fmaf(qb.z, kf[6], d); d = fmaf(qb.w, kf[7], d);
+                        s[r] = d;
+                    }
                 }
             }
         }
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            const float wm = warp_max(page >= 0 ? s[r] : -INFINITY);
+            if (lane == 0) sred[r * GS_WARPS + warp] = wm;
+        }
+        __syncthreads();
+        float corr[REP];
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            float tm = sred[r * GS_WARPS];
+#pragma unroll
+            for (int w = 1; w < GS_WARPS; ++w) tm = fmaxf(tm, sred[r * GS_WARPS + w]);
+            const float n = fmaxf(m[r], tm);
+            corr[r] = m[r] == -INFINITY ? 0.f : expf(m[r] - n);
+            m[r] = n;
+            sp[r * GS_TILE + threadIdx.x] = page >= 0 ? expf(s[r] - n) : 0.f;
+        }
+        srow[threadIdx.x] = page >= 0 ? (long long)(cache_values(pool, cache, page, kvh, key % ps) - pool) : -1;
+        __syncthreads();
+        // ---- values: this warp's keys of the tile
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            l[r] *= corr[r];
+#pragma unroll
+            for (int p = 0; p < GS_VPASS; ++p)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) acc[r][p][x] *= corr[r];
+        }
+        const int tile_n = min(GS_TILE, total - i0);
+#pragma unroll 4
+        for (int j = warp; j < tile_n; j += GS_WARPS) {
+            const long long off = srow[j];
+            if (off < 0) continue;                         // (the same in all lanes of the warp)
+            float4 vv[GS_VPASS];
+#pragma unroll
+            for (int p = 0; p < GS_VPASS; ++p)
+                vv[p] = p * 128 + e_v < vd ? load4_cg(pool + off + p * 128 + e_v) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < REP; ++r) {
+                const float w = sp[r * GS_TILE + j];
+                l[r] += w;
+#pragma unroll
+                for (int p = 0; p < GS_VPASS; ++p) {
+                    acc[r][p][0] = fmaf(w, vv[p].x, acc[r][p][0]);
+                    acc[r][p][1] = fmaf(w, vv[p].y, acc[r][p][1]);
+                    acc[r][p][2] = fmaf(w, vv[p].z, acc[r][p][2]);
+                    acc[r][p][3] = fmaf(w, vv[p].w, acc[r][p][3]);
+                }
+            }
+        }
+        // (the next tile's first barrier stands between these reads of sp and srow and their next writes)
     }
-    const int ld = vd + 2;
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
-        if (r >= rep) continue;
-        float* dst = gs_smem + ((size_t)warp * REP + r) * ld;
+        float* dst = so + ((size_t)warp * REP + r) * vd;
 #pragma unroll
         for (int p = 0; p < GS_VPASS; ++p)
 #pragma unroll
             for (int x = 0; x < 4; ++x)
-                if (p * 128 + e_k + x < vd) dst[p * 128 + e_k + x] = acc[r][p][x];
-        if (lane == 0) { dst[vd] = m[r]; dst[vd + 1] = l[r]; }
+                if (p * 128 + e_v + x < vd) dst[p * 128 + e_v + x] = acc[r][p][x];
+        if (lane == 0) sl[warp * REP + r] = l[r];
     }
     __syncthreads();
     const bf16* gate = reinterpret_cast<const bf16*>(epi.gate);
     for (int idx = threadIdx.x; idx < rep * vd; idx += GS_THREADS) {
         const int r = idx / vd, e = idx % vd;
-        float M = has_sink ? sink : -INFINITY;
-        for (int w = 0; w < GS_WARPS; ++w) M = fmaxf(M, gs_smem[((size_t)w * REP + r) * ld + vd]);
-        float L = has_sink ? expf(sink - M) : 0.f, O = 0.f;
+        // m[] is indexed by a runtime head here: every thread holds the same maxima, pick by comparison
+        float mr = -INFINITY;
+#pragma unroll
+        for (int rr = 0; rr < REP; ++rr)
+            if (rr == r) mr = m[rr];
+        float L = 0.f, O = 0.f;
         for (int w = 0; w < GS_WARPS; ++w) {
-            const float* src = gs_smem + ((size_t)w * REP + r) * ld;
-            const float mw = src[vd];
-            if (mw == -INFINITY) continue;
-            const float c = expf(mw - M);
-            L = fmaf(src[vd + 1], c, L);
-            O = fmaf(src[e], c, O);
+            L += sl[w * REP + r];
+            O += so[((size_t)w * REP + r) * vd + e];
+        }
+        if (has_sink) {
+            const float n = fmaxf(mr, sink);
+            const float c = mr == -INFINITY ? 0.f : expf(mr - n);
+            L = fmaf(L, c, expf(sink - n));
+            O *= c;
         }
         float o = L > 0.f ? O * epi.out_scale / L : 0.f;
         const int h = h0 + r;
@@ -348,8 +406,14 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     }
 }
 
+static size_t gqa_single_smem(int rep_t, int dim, int vd) {
+    return (size_t)GS_TILE * sizeof(long long) +
+           ((size_t)rep_t * dim + (size_t)rep_t * GS_TILE + 2 * (size_t)rep_t * GS_WARPS + (size_t)GS_WARPS * rep_t * vd) *
+               sizeof(float);
+}
+
 ST_EXPORT int st_gqa_attention_single_applies(int nh, int nkv, int dim, int vd) {
-    return nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 8 && dim > 0 && vd > 0 && dim % 4 == 0 && vd % 4 == 0 &&
+    return nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 8 && dim > 0 && vd > 0 && dim % 8 == 0 && vd % 4 == 0 &&
            dim <= 128 && vd <= 128 * GS_VPASS;
 }
 
@@ -358,7 +422,7 @@ static int launch_gqa_single(const void* q, const void* pool, const DiffCache& c
                              const int* positions, const int* seq_of_token, const int* slots, const int* block_table,
                              int n_tokens, int nh, float scale, const GqaMask& mask, int has_sink, float sink,
                              const GqaEpilogue& epi, int* status, cudaStream_t s) {
-    const size_t smem = (size_t)GS_WARPS * REP * (c.vd + 2) * sizeof(float);
+    const size_t smem = gqa_single_smem(REP, c.kd, c.vd);
     auto kern = gqa_attention_single_kernel<REP>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -23,7 +23,8 @@ TIMED = ("embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gathe
          "linear_parts", "argmax", "sample", "conv_residual", "conv_state_update", "norm_add", "gated_act",
          "diff_qkv_prepare", "diff_attention_plain", "diff_attention_single", "diff_attention_tiles", "hgrn2_scan",
          "latent_prepare", "latent_q_rotate", "latent_attention", "gemm_heads", "moe_route", "moe_sort", "gemm_experts",
-         "moe_combine", "concat_rows", "scale_softcap")
+         "moe_combine", "concat_rows", "scale_softcap", "gqa_prepare", "gqa_attention_plain", "gqa_attention_single",
+         "gqa_attention_tiles", "delta_rule", "gated_clamped_act")
 
 _originals: Dict[str, object] = {}
 _events: List[Tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
