@@ -22,6 +22,7 @@
 
 #define DR_MAX_TAPS 8
 #define DR_PREP_THREADS 256
+#define DR_EARLY_TOKENS 128   // steps of at most this many tokens let the next kernel's blocks in early
 #define DR_UNIT_PASSES 8      // a warp's lanes cover a head of up to 32 * DR_UNIT_PASSES channels
 
 struct DeltaShape {
@@ -51,7 +52,11 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, DeltaShape sh, cons
                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                      const int* __restrict__ q_start, const int* __restrict__ slots) {
     ST_PDL_WAIT();
-    ST_PDL_TRIGGER();
+    // In a step of few tokens the recurrence's blocks may come in at once.  In a long portion they come in when this
+    // grid is all but done: let in early, they were placed on the few multiprocessors that had room beside this
+    // grid's blocks, many to each, and the walk over 2048 tokens took nearly twice as long (measured).
+    const bool early = gridDim.x <= DR_EARLY_TOKENS;
+    if (early) ST_PDL_TRIGGER();
     const int t = blockIdx.x;
     const int pos = positions[t];
     if (pos < 0) return;
@@ -117,6 +122,7 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, DeltaShape sh, cons
         const float dt = softplusf_(z + dt_bias[c]);
         dst[sh.pd() + c] = expf(-expf(a_log[c / dim]) * dt);
     }
+    if (!early) ST_PDL_TRIGGER();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -134,9 +140,8 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, DeltaShape sh, cons
 #define DS_CHUNK 8
 #define DS_STAGES 3
 
-__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
+__device__ __forceinline__ void cp_async4s(uint32_t dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src));
 }
 __device__ __forceinline__ void ds_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void ds_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
@@ -157,7 +162,6 @@ delta_scan_kernel(const float* __restrict__ prep, DeltaShape sh, float* __restri
     using M = DeltaScanSmem<L, R>;
     extern __shared__ __align__(16) float ds_smem[];
     ST_PDL_WAIT();
-    ST_PDL_TRIGGER();
     const int b = blockIdx.x, h = blockIdx.y;
     const int first = q_start[b], n = q_start[b + 1] - first;
     if (n <= 0 || positions[first] < 0) return;            // padding of a fixed-shape step
@@ -178,23 +182,46 @@ delta_scan_kernel(const float* __restrict__ prep, DeltaShape sh, float* __restri
     for (int i = threadIdx.x; i < DS_STAGES * DS_CHUNK * M::ROW; i += DS_THREADS) ds_smem[i] = 0.f;
     __syncthreads();
     const int n_chunks = (n + DS_CHUNK - 1) / DS_CHUNK;
+    // What this thread copies for every token is fixed for the launch: JN key dimensions (their k, q and decay) and
+    // one of the block's values or beta.  The places are worked out once; per token a copy is then an addition.
+    constexpr int JN = (M::DP + DS_THREADS - 1) / DS_THREADS;
+    int src_k[JN], src_q[JN], src_d[JN];
+    uint32_t dst_at[JN];
+    const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(ds_smem);
+#pragma unroll
+    for (int ji = 0; ji < JN; ++ji) {
+        const int j = threadIdx.x + ji * DS_THREADS;
+        src_k[ji] = j < dim ? sh.pk() + g * dim + j : -1;
+        src_q[ji] = sh.pq() + g * dim + j;
+        src_d[ji] = sh.pd() + h * dim + j;
+        dst_at[ji] = (uint32_t)((j % R) * L + j / R) * 4u;
+    }
+    int src_x = -1;                                        // the value of one of the block's columns, or beta
+    if (threadIdx.x < M::COLS) {
+        if (col0 + threadIdx.x < vd) src_x = sh.pv() + h * vd + col0 + threadIdx.x;
+    } else if (threadIdx.x == M::COLS) {
+        src_x = sh.pb() + h;
+    }
+    const uint32_t dst_x = (uint32_t)(3 * M::DP + threadIdx.x) * 4u;
     auto stage_chunk = [&](int c) {
-        float* dst0 = ds_smem + (size_t)(c % DS_STAGES) * DS_CHUNK * M::ROW;
+        uint32_t dst = smem0 + (uint32_t)((c % DS_STAGES) * DS_CHUNK * M::ROW) * 4u;
         const int t_end = min(DS_CHUNK, n - c * DS_CHUNK);
-        for (int t = 0; t < t_end; ++t) {
-            const float* row = p + (size_t)(c * DS_CHUNK + t) * row_len;
-            float* dst = dst0 + t * M::ROW;
-            for (int j = threadIdx.x; j < dim; j += DS_THREADS) {
-                const int at = (j % R) * L + j / R;
-                cp_async4(dst + at, row + sh.pk() + g * dim + j);
-                cp_async4(dst + M::DP + at, row + sh.pq() + g * dim + j);
-                cp_async4(dst + 2 * M::DP + at, row + sh.pd() + h * dim + j);
+        const float* row = p + (size_t)(c * DS_CHUNK) * row_len;
+#pragma unroll
+        for (int t = 0; t < DS_CHUNK; ++t) {
+            if (t < t_end) {
+#pragma unroll
+                for (int ji = 0; ji < JN; ++ji) {
+                    if (src_k[ji] >= 0) {
+                        cp_async4s(dst + dst_at[ji], row + src_k[ji]);
+                        cp_async4s(dst + (uint32_t)M::DP * 4u + dst_at[ji], row + src_q[ji]);
+                        cp_async4s(dst + (uint32_t)M::DP * 8u + dst_at[ji], row + src_d[ji]);
+                    }
+                }
+                if (src_x >= 0) cp_async4s(dst + dst_x, row + src_x);
             }
-            if (threadIdx.x < M::COLS) {
-                if (col0 + threadIdx.x < vd) cp_async4(dst + 3 * M::DP + threadIdx.x, row + sh.pv() + h * vd + col0 + threadIdx.x);
-            } else if (threadIdx.x == M::COLS) {
-                cp_async4(dst + 3 * M::DP + M::COLS, row + sh.pb() + h);
-            }
+            row += row_len;
+            dst += (uint32_t)M::ROW * 4u;
         }
     };
 #pragma unroll
@@ -202,6 +229,9 @@ delta_scan_kernel(const float* __restrict__ prep, DeltaShape sh, float* __restri
         if (c < n_chunks) stage_chunk(c);
         ds_commit();
     }
+    float* o_at = o_out + (size_t)first * H * vd + h * vd + col;
+    const size_t o_step = (size_t)H * vd;
+    const bool writes_o = live && sub == 0;
     float kq[R], qq[R], dd[R], v, beta;
     auto fetch = [&](const float* row) {
 #pragma unroll
@@ -247,9 +277,13 @@ delta_scan_kernel(const float* __restrict__ prep, DeltaShape sh, float* __restri
             const float u = beta_now * (v_now - sk);
 #pragma unroll
             for (int r = 0; r < R; ++r) s[r] = fmaf(k_[r], u, s[r]);
-            if (live && sub == 0) o_out[(size_t)(first + c * DS_CHUNK + t) * H * vd + h * vd + col] = fmaf(u, kdq, sq);
+            if (writes_o) *o_at = fmaf(u, kdq, sq);
+            o_at += o_step;
         }
     }
+    // The successor's blocks are let in only now: while they wait for this grid on the same multiprocessors, the
+    // walk over a long portion was measured to take nearly twice as long.
+    ST_PDL_TRIGGER();
     ds_wait<0>();
     if (write_state && live) {
 #pragma unroll
@@ -287,6 +321,13 @@ delta_output_kernel(const float* __restrict__ o, const float* __restrict__ proj,
     }
 }
 
+// 0: the launcher chooses the lanes per column of the recurrence; 8, 16 or 32: this many (for tests and tuning).
+static int ds_forced_lanes = 0;
+ST_EXPORT int st_delta_rule_set_lanes(int lanes) {
+    if (lanes != 0 && lanes != 8 && lanes != 16 && lanes != 32) return ST_ERR_BAD_ARG;
+    ds_forced_lanes = lanes;
+    return 0;
+}
 ST_EXPORT long long st_delta_rule_scratch_floats(int n_tokens, int H, int G, int dim, int vd) {
     return (long long)n_tokens * ((long long)2 * G * dim + (long long)H * vd + (long long)H * dim + H + (long long)H * vd);
 }
@@ -342,10 +383,31 @@ ST_EXPORT int st_delta_rule(const float* proj, int ld, int q_off, int b_off, int
                            dim3(n_seqs, H, (vd + DS_THREADS / L - 1) / (DS_THREADS / L)), dim3(DS_THREADS), smem, s, \
                            (const float*)prep, sh, state, write_state, o, positions, q_start, slots);                \
     } while (0)
-        if (dim <= 32) DS_LAUNCH(8, 4);
-        else if (dim <= 64) DS_LAUNCH(8, 8);
-        else if (dim <= 128) DS_LAUNCH(8, 16);
-        else DS_LAUNCH(32, 8);
+        // Lanes per column.  A token's step is a chain of dependent instructions, so a launch is as fast as its
+        // blocks are many: with few requests and heads, more lanes per column (fewer rows each, more stages of
+        // shuffles) spread the state over more multiprocessors.  Eight lanes once the blocks fill the device twice.
+        int lanes = ds_forced_lanes;
+        if (!lanes) {
+            const long long cols8 = (vd + DS_THREADS / 8 - 1) / (DS_THREADS / 8);
+            const long long blocks8 = (long long)n_seqs * H * cols8;
+            lanes = blocks8 >= 2 * st_sm_count() ? 8 : blocks8 * 2 >= 2 * st_sm_count() ? 16 : 32;
+        }
+        if (lanes == 8 && dim > 128) lanes = 16;
+        if (lanes == 8) {
+            if (dim <= 32) DS_LAUNCH(8, 4);
+            else if (dim <= 64) DS_LAUNCH(8, 8);
+            else DS_LAUNCH(8, 16);
+        } else if (lanes == 16) {
+            if (dim <= 32) DS_LAUNCH(16, 2);
+            else if (dim <= 64) DS_LAUNCH(16, 4);
+            else if (dim <= 128) DS_LAUNCH(16, 8);
+            else DS_LAUNCH(16, 16);
+        } else {
+            if (dim <= 32) DS_LAUNCH(32, 1);
+            else if (dim <= 64) DS_LAUNCH(32, 2);
+            else if (dim <= 128) DS_LAUNCH(32, 4);
+            else DS_LAUNCH(32, 8);
+        }
 #undef DS_LAUNCH
         if (rc) return rc;
     }

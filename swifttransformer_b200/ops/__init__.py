@@ -1180,6 +1180,12 @@ def delta_rule_scratch(n_tokens: int, H: int, G: int, dim: int, vd: int) -> int:
     return int(lib().st_delta_rule_scratch_floats(n_tokens, H, G, dim, vd))
 
 
+def delta_rule_set_lanes(lanes: int) -> None:
+    """How many lanes share a column of the state in the recurrence: 8, 16 or 32, or 0 for the launcher's own choice by
+    the number of blocks a step gives (the default)."""
+    _check(lib().st_delta_rule_set_lanes(int(lanes)), "delta_rule_set_lanes")
+
+
 def delta_rule(proj: torch.Tensor, b_off: int, a_off: int, g_off: int, conv_w: torch.Tensor, conv_state: torch.Tensor,
                w_a2: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, w_g2: torch.Tensor, norm_w: torch.Tensor,
                eps: float, out_scale: float, state: torch.Tensor, write_state: bool, single_tokens: bool,

@@ -159,6 +159,23 @@ def test_delta_rule_in_portions_and_token_by_token(dtype, shape):
         assert err.max() < tol, (sizes, int(np.argmax(err > tol)), float(err.max()))
 
 
+@pytest.mark.parametrize("lanes", [8, 16, 32])
+@pytest.mark.parametrize("shape", DELTA_SHAPES)
+def test_delta_rule_with_every_layout_of_the_state(lanes, shape):
+    from swifttransformer_b200 import ops
+    H, G, d, dv, taps, rank = shape
+    T = 45
+    w, h = delta_case(H, G, d, dv, taps, rank, seed=H * 10 + d + lanes, T=T, slow_decay=True)
+    ref = 0.7 * pn.gated_delta(h, w, "m.", dict(heads=H, kv_heads=G, dim=d, vdim=dv, conv=taps), 1e-5)
+    ops.delta_rule_set_lanes(lanes)
+    try:
+        for sizes in ((T,), (9, 1, 1, 2, 30, 1, 1)):
+            got, _, _ = run_delta(w, h, H, G, d, dv, taps, "float32", portions(T, sizes))
+            assert np.abs(got - ref).max() < 3e-5 * np.abs(ref).max(), (lanes, sizes)
+    finally:
+        ops.delta_rule_set_lanes(0)
+
+
 def test_delta_rule_remembers_a_far_token_and_forgets_with_decay():
     """One token writes a value along a key; fifty tokens later a query along that key reads it back when the
     decays are near one, and reads nothing when they are strong."""
