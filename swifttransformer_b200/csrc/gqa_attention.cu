@@ -222,33 +222,47 @@ ST_EXPORT int st_gqa_attention_plain(const void* q, const void* pool, long long 
 //            (GS_TILE rows are on their way together) and takes the dot products with the group's queries, which
 //            stand in shared memory as scaled floats; the tile's maximum per head is found over the block, and the
 //            weights exp(s - m) go to shared memory with the address of the key's value row;
-//   values   warp w takes keys w, w + GS_WARPS, .. of the tile, its lanes side by side along the value row (four
-//            neighbouring elements each: vd <= 128 * GS_VPASS), several rows in flight.
+//   values   the warps share the tile's keys, their lanes side by side along the value row (a 16-byte piece of eight
+//            elements each: vd <= 256; rows of up to 128 elements take half a warp, so a warp walks two keys at
+//            once), many rows in flight.
 // The running maximum is the block's, so the warps' sums only have to be added at the end, where the extra term
 // joins and a thread per (head, value dimension) scales, gates and stores.  What is added in which order depends
-// on the key's number only, so a token's result is the same whatever else the step holds.
-#define GS_THREADS 256
-#define GS_WARPS (GS_THREADS / 32)
-#define GS_TILE GS_THREADS
-#define GS_VPASS 2
+// on the key's number and on the block's shape (which the launcher picks by the step's size), so a token's result
+// does not depend on the other tokens of the step beyond the rounding of sums taken in another order.
+// Threads of a block (= keys of a tile) and value rows a warp asks for at once, by the query heads a block serves:
+// with one or two heads the registers allow sixteen warps, four per scheduler, which hide one another's waits.
+template <int REP> struct GsShape {
+    static constexpr int THREADS = REP <= 2 ? 512 : 256;
+    static constexpr int VB = REP == 1 ? 16 : (REP <= 4 ? 8 : 4);
+};
 #define GS_KPIECES 8      // 16-byte pieces of a key row asked for at once (64 dimensions)
 
+// every 128-byte line of a row of n bfloat16 elements
+__device__ __forceinline__ void gs_prefetch_row(const bf16* row, int n) {
+    const char* p = reinterpret_cast<const char*>(row);
+    const char* last = p + 2 * n - 1;
+    for (const char* a = p; a < last; a += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(last));
+}
+
 template <int REP>
-__global__ void __launch_bounds__(GS_THREADS)
+__global__ void __launch_bounds__(GsShape<REP>::THREADS)
 gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, DiffCache cache,
                             bf16* __restrict__ out, const int* __restrict__ items, const int* __restrict__ positions,
                             const int* __restrict__ seq_of_token, const int* __restrict__ slots,
-                            const int* __restrict__ block_table, int nh, float scale, GqaMask mask, int has_sink,
-                            float sink, GqaEpilogue epi, int* __restrict__ status) {
+                            const int* __restrict__ block_table, int nh, int hb, float scale, GqaMask mask,
+                            int has_sink, float sink, GqaEpilogue epi, int* __restrict__ status) {
+    constexpr int GS_THREADS = GsShape<REP>::THREADS, GS_WARPS = GS_THREADS / 32, GS_TILE = GS_THREADS;
     extern __shared__ __align__(16) unsigned char gs_raw[];
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
-    const int t = items ? items[blockIdx.x] : blockIdx.x, kvh = blockIdx.y;
+    const int t = items ? items[blockIdx.x] : blockIdx.x;
     if (t < 0) return;
     const int pos = positions[t];
     if (pos < 0) return;
     const int nkv = cache.nkv, vd = cache.vd, dim = cache.kd, ps = cache.page_size;
-    const int rep = nh / nkv, h0 = kvh * rep;
+    // the block's query heads: hb neighbours of one group (hb divides the group's size, hb <= REP)
+    const int rep = hb, h0 = blockIdx.y * hb, kvh = h0 / (nh / nkv);
     long long* srow = reinterpret_cast<long long*>(gs_raw);             // [GS_TILE] value rows (element offsets), -1: none
     float* sq = reinterpret_cast<float*>(srow + GS_TILE);               // [REP][dim] queries times scale
     float* sp = sq + REP * dim;                                         // [REP][GS_TILE] weights
@@ -263,16 +277,18 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         const int r = i / dim;
         sq[i] = r < rep ? load1_cg(q + ((size_t)t * nh + h0) * dim + i) * scale : 0.f;
     }
-    const int e_v = 4 * lane;
-    float acc[REP][GS_VPASS][4], m[REP], l[REP];
+    // value rows: a lane owns eight neighbouring dimensions (one 16-byte piece).  Rows of up to 128 dimensions take
+    // half a warp, and the two halves walk different keys; wider rows (up to 256) take the whole warp.
+    const bool wide = vd > 128;
+    const int half = wide ? 0 : lane >> 4, keys_per_step = wide ? 1 : 2;
+    const int e_v = 8 * (wide ? lane : (lane & 15));
+    float acc[REP][8], m[REP], l[REP];
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
         m[r] = -INFINITY;
         l[r] = 0.f;
 #pragma unroll
-        for (int p = 0; p < GS_VPASS; ++p)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) acc[r][p][x] = 0.f;
+        for (int x = 0; x < 8; ++x) acc[r][x] = 0.f;
     }
     __syncthreads();
     const int pieces = dim / 8;
@@ -288,6 +304,15 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         float s[REP];
 #pragma unroll
         for (int r = 0; r < REP; ++r) s[r] = 0.f;
+        // Asked into the second-level cache now, so that they are near when their turn comes: this key's value row
+        // (read in the second phase) and the key row this thread takes in the next tile.
+        if (page >= 0) gs_prefetch_row(cache_values(pool, cache, page, kvh, key % ps), vd);
+        if (i + GS_TILE < total) {
+            const int i_n = i + GS_TILE;
+            const int key_n = i_n < head_end ? i_n : lo + (i_n - head_end);
+            const int page_n = bt[key_n / ps];
+            if (page_n >= 0) gs_prefetch_row(cache_keys(pool, cache, page_n, kvh, key_n % ps), dim);
+        }
         if (page >= 0) {
             const uint4* kp = reinterpret_cast<const uint4*>(cache_keys(pool, cache, page, kvh, key % ps));
             for (int c0 = 0; c0 < pieces; c0 += GS_KPIECES) {
@@ -341,29 +366,38 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         for (int r = 0; r < REP; ++r) {
             l[r] *= corr[r];
 #pragma unroll
-            for (int p = 0; p < GS_VPASS; ++p)
-#pragma unroll
-                for (int x = 0; x < 4; ++x) acc[r][p][x] *= corr[r];
+            for (int x = 0; x < 8; ++x) acc[r][x] *= corr[r];
         }
         const int tile_n = min(GS_TILE, total - i0);
-#pragma unroll 4
-        for (int j = warp; j < tile_n; j += GS_WARPS) {
-            const long long off = srow[j];
-            if (off < 0) continue;                         // (the same in all lanes of the warp)
-            float4 vv[GS_VPASS];
+        // a warp's keys go VB steps at a time: all their value rows are asked for before the first is used, so that
+        // a block keeps tens of kilobytes on their way (the rows, not the arithmetic, set the pace)
+        constexpr int VB = GsShape<REP>::VB;
+        const int stride = GS_WARPS * keys_per_step;
+        for (int j0 = warp * keys_per_step + half; j0 < tile_n + half; j0 += stride * VB) {
+            uint4 raw[VB];
+            bool has[VB];
 #pragma unroll
-            for (int p = 0; p < GS_VPASS; ++p)
-                vv[p] = p * 128 + e_v < vd ? load4_cg(pool + off + p * 128 + e_v) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int b = 0; b < VB; ++b) {
+                const int j = j0 + b * stride;
+                const long long off = j < tile_n ? srow[j] : -1;
+                has[b] = off >= 0;
+                raw[b] = (has[b] && e_v < vd) ? __ldcg(reinterpret_cast<const uint4*>(pool + off + e_v))
+                                              : make_uint4(0u, 0u, 0u, 0u);
+            }
 #pragma unroll
-            for (int r = 0; r < REP; ++r) {
-                const float w = sp[r * GS_TILE + j];
-                l[r] += w;
+            for (int b = 0; b < VB; ++b) {
+                if (!has[b]) continue;
+                const int j = j0 + b * stride;
+                const uint32_t w4[4] = {raw[b].x, raw[b].y, raw[b].z, raw[b].w};
 #pragma unroll
-                for (int p = 0; p < GS_VPASS; ++p) {
-                    acc[r][p][0] = fmaf(w, vv[p].x, acc[r][p][0]);
-                    acc[r][p][1] = fmaf(w, vv[p].y, acc[r][p][1]);
-                    acc[r][p][2] = fmaf(w, vv[p].z, acc[r][p][2]);
-                    acc[r][p][3] = fmaf(w, vv[p].w, acc[r][p][3]);
+                for (int r = 0; r < REP; ++r) {
+                    const float w = sp[r * GS_TILE + j];
+                    l[r] += w;
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        acc[r][2 * x] = fmaf(w, __uint_as_float(w4[x] << 16), acc[r][2 * x]);
+                        acc[r][2 * x + 1] = fmaf(w, __uint_as_float(w4[x] & 0xffff0000u), acc[r][2 * x + 1]);
+                    }
                 }
             }
         }
@@ -371,12 +405,17 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     }
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
+        if (!wide) {                                   // the two halves of the warp walked different keys
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 16);
+#pragma unroll
+            for (int x = 0; x < 8; ++x) acc[r][x] += __shfl_xor_sync(0xffffffffu, acc[r][x], 16);
+        }
         float* dst = so + ((size_t)warp * REP + r) * vd;
+        if (half == 0) {
 #pragma unroll
-        for (int p = 0; p < GS_VPASS; ++p)
-#pragma unroll
-            for (int x = 0; x < 4; ++x)
-                if (p * 128 + e_v + x < vd) dst[p * 128 + e_v + x] = acc[r][p][x];
+            for (int x = 0; x < 8; ++x)
+                if (e_v + x < vd) dst[e_v + x] = acc[r][x];
+        }
         if (lane == 0) sl[warp * REP + r] = l[r];
     }
     __syncthreads();
@@ -406,31 +445,31 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     }
 }
 
-static size_t gqa_single_smem(int rep_t, int dim, int vd) {
-    return (size_t)GS_TILE * sizeof(long long) +
-           ((size_t)rep_t * dim + (size_t)rep_t * GS_TILE + 2 * (size_t)rep_t * GS_WARPS + (size_t)GS_WARPS * rep_t * vd) *
-               sizeof(float);
+static size_t gqa_single_smem(int rep_t, int threads, int dim, int vd) {
+    const size_t tile = threads, warps = threads / 32;
+    return tile * sizeof(long long) +
+           ((size_t)rep_t * dim + (size_t)rep_t * tile + 2 * (size_t)rep_t * warps + warps * rep_t * vd) * sizeof(float);
 }
 
 ST_EXPORT int st_gqa_attention_single_applies(int nh, int nkv, int dim, int vd) {
-    return nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 8 && dim > 0 && vd > 0 && dim % 8 == 0 && vd % 4 == 0 &&
-           dim <= 128 && vd <= 128 * GS_VPASS;
+    return nh > 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 8 && dim > 0 && vd > 0 && dim % 8 == 0 && vd % 8 == 0 &&
+           dim <= 128 && vd <= 256;
 }
 
 template <int REP>
 static int launch_gqa_single(const void* q, const void* pool, const DiffCache& c, void* out, const int* items,
                              const int* positions, const int* seq_of_token, const int* slots, const int* block_table,
-                             int n_tokens, int nh, float scale, const GqaMask& mask, int has_sink, float sink,
+                             int n_tokens, int nh, int hb, float scale, const GqaMask& mask, int has_sink, float sink,
                              const GqaEpilogue& epi, int* status, cudaStream_t s) {
-    const size_t smem = gqa_single_smem(REP, c.kd, c.vd);
+    const size_t smem = gqa_single_smem(REP, GsShape<REP>::THREADS, c.kd, c.vd);
     auto kern = gqa_attention_single_kernel<REP>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return st_launch_pdl("gqa_single", kern, dim3(n_tokens, c.nkv), dim3(GS_THREADS), smem, s, (const bf16*)q,
-                         (const bf16*)pool, c, (bf16*)out, items, positions, seq_of_token, slots, block_table, nh, scale,
-                         mask, has_sink, sink, epi, status);
+    return st_launch_pdl("gqa_single", kern, dim3(n_tokens, nh / hb), dim3(GsShape<REP>::THREADS), smem, s, (const bf16*)q,
+                         (const bf16*)pool, c, (bf16*)out, items, positions, seq_of_token, slots, block_table, nh, hb,
+                         scale, mask, has_sink, sink, epi, status);
 }
 
 // bfloat16 only; `items` as for the plain kernel
@@ -447,12 +486,19 @@ ST_EXPORT int st_gqa_attention_single(const void* q, const void* pool, long long
     const GqaMask mask = {window, keep_first};
     const GqaEpilogue epi = {gate, gate_ld, out_scale};
     cudaStream_t s = (cudaStream_t)stream;
+    // Query heads per block: the whole group when that gives blocks enough to fill the device twice (a key or value
+    // row is then fetched once for the group), else the largest part of the group that does, down to one head; the
+    // other blocks of a group find the rows in the second-level cache.  A head's result differs between the cases only
+    // in how its keys are dealt to warps, that is in the order of additions.
     const int rep = nh / nkv;
-#define GS_ARGS q, pool, c, out, items, positions, seq_of_token, slots, block_table, n_tokens, nh, scale, mask, has_sink, sink, \
-                epi, status, s
-    if (rep == 1) return launch_gqa_single<1>(GS_ARGS);
-    if (rep == 2) return launch_gqa_single<2>(GS_ARGS);
-    if (rep <= 4) return launch_gqa_single<4>(GS_ARGS);
+    int hb = 1;
+    for (int d = rep; d >= 1; --d)
+        if (rep % d == 0 && (long long)n_tokens * (nh / d) >= 2LL * st_sm_count()) { hb = d; break; }
+#define GS_ARGS q, pool, c, out, items, positions, seq_of_token, slots, block_table, n_tokens, nh, hb, scale, mask, has_sink, \
+                sink, epi, status, s
+    if (hb == 1) return launch_gqa_single<1>(GS_ARGS);
+    if (hb == 2) return launch_gqa_single<2>(GS_ARGS);
+    if (hb <= 4) return launch_gqa_single<4>(GS_ARGS);
     return launch_gqa_single<8>(GS_ARGS);
 #undef GS_ARGS
 }

@@ -1264,7 +1264,7 @@ def gqa_attention_single(q: torch.Tensor, pool: torch.Tensor, layer: int, out: t
     """The same attention token by token in bfloat16, one block per (token, key/value head) for all the query heads
     that read it; ``items`` as for the plain kernel."""
     if not (q.dtype == torch.bfloat16 and bool(lib().st_gqa_attention_single_applies(nh, nkv, dim, vd))):
-        raise KernelError("gqa_attention_single: bfloat16, dim a multiple of 8, vd of 4, dim <= 128, vd <= 256, at most "
+        raise KernelError("gqa_attention_single: bfloat16, dim and vd multiples of 8, dim <= 128, vd <= 256, at most "
                           "eight query heads per key/value head")
     assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
     stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink,
