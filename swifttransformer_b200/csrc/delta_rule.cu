@@ -41,6 +41,37 @@ struct DeltaShape {
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ float siluf_(float z) { return z / (1.f + expf(-z)); }
 
+// sum_r x[r] * w[r] in the order of r, the weights fetched in 16-byte pieces where the row allows it
+#define DR_RANK_SMEM 256      // low-rank inputs of up to this many numbers wait in shared memory
+template <typename TW>
+__device__ __forceinline__ float lowrank_dot(const float* x, const TW* __restrict__ w, int rank) {
+    float z = 0.f;
+    if constexpr (sizeof(TW) == 2) {
+        if ((rank & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+            for (int r = 0; r < rank; r += 8) {
+                const uint4 u = __ldg(reinterpret_cast<const uint4*>(w + r));
+                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    z = fmaf(x[r + 2 * i], __uint_as_float(w4[i] << 16), z);
+                    z = fmaf(x[r + 2 * i + 1], __uint_as_float(w4[i] & 0xffff0000u), z);
+                }
+            }
+            return z;
+        }
+    } else {
+        if ((rank & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+            for (int r = 0; r < rank; r += 4) {
+                const float4 u = __ldg(reinterpret_cast<const float4*>(w + r));
+                z = fmaf(x[r], u.x, z); z = fmaf(x[r + 1], u.y, z); z = fmaf(x[r + 2], u.z, z); z = fmaf(x[r + 3], u.w, z);
+            }
+            return z;
+        }
+    }
+    for (int r = 0; r < rank; ++r) z = fmaf(x[r], to_f32(w[r]), z);
+    return z;
+}
+
 // conv_w: float [2*G*dim + H*vd, taps] in the projection's order q | k | v; state: [slots, taps-1, channels]
 // float, the last taps-1 projected rows of every request (read here; with move_state, in steps where every request
 // brings one token, also moved on here: the thread that reads a channel's state is the only one that writes it).
@@ -115,10 +146,15 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, DeltaShape sh, cons
             dst[sh.pb() + h] = 1.f / (1.f + expf(-__ldcg(row + sh.b_off + h)));
     }
     // decays: the low-rank step size, one thread per (head, key channel)
+    __shared__ float xs_a[DR_RANK_SMEM];
+    const float* xa = row + sh.a_off;
+    if (sh.rank_a <= DR_RANK_SMEM) {
+        for (int r = threadIdx.x; r < sh.rank_a; r += blockDim.x) xs_a[r] = __ldcg(xa + r);
+        __syncthreads();
+        xa = xs_a;
+    }
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H * dim; c += blockDim.x * gridDim.y) {
-        float z = 0.f;
-        const TW* w = w_a2 + (size_t)c * sh.rank_a;
-        for (int r = 0; r < sh.rank_a; ++r) z = fmaf(__ldcg(row + sh.a_off + r), to_f32(w[r]), z);
+        const float z = lowrank_dot(xa, w_a2 + (size_t)c * sh.rank_a, sh.rank_a);
         const float dt = softplusf_(z + dt_bias[c]);
         dst[sh.pd() + c] = expf(-expf(a_log[c / dim]) * dt);
     }
@@ -312,11 +348,15 @@ delta_output_kernel(const float* __restrict__ o, const float* __restrict__ proj,
     }
     ss = block_sum(ss, scratch);
     const float inv = rsqrtf(ss / (float)vd + eps) * out_scale;
+    __shared__ float xs_g[DR_RANK_SMEM];
     const float* g1 = proj + (size_t)t * ld + sh.g_off;
+    if (sh.rank_g <= DR_RANK_SMEM) {
+        for (int r = threadIdx.x; r < sh.rank_g; r += blockDim.x) xs_g[r] = __ldcg(g1 + r);
+        __syncthreads();
+        g1 = xs_g;
+    }
     for (int e = threadIdx.x; e < vd; e += blockDim.x) {
-        float z = 0.f;
-        const T* w = w_g2 + (size_t)(h * vd + e) * sh.rank_g;
-        for (int r = 0; r < sh.rank_g; ++r) z = fmaf(__ldcg(g1 + r), to_f32(w[r]), z);
+        const float z = lowrank_dot(g1, w_g2 + (size_t)(h * vd + e) * sh.rank_g, sh.rank_g);
         out[((size_t)t * sh.H + h) * vd + e] = from_f32<T>(__ldcg(orow + e) * inv * norm_w[e] / (1.f + expf(-z)));
     }
 }

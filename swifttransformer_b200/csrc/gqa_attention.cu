@@ -486,14 +486,14 @@ ST_EXPORT int st_gqa_attention_single(const void* q, const void* pool, long long
     const GqaMask mask = {window, keep_first};
     const GqaEpilogue epi = {gate, gate_ld, out_scale};
     cudaStream_t s = (cudaStream_t)stream;
-    // Query heads per block: the whole group when that gives blocks enough to fill the device twice (a key or value
+    // Query heads per block: the whole group when that gives blocks for three quarters of the device (a key or value
     // row is then fetched once for the group), else the largest part of the group that does, down to one head; the
     // other blocks of a group find the rows in the second-level cache.  A head's result differs between the cases only
     // in how its keys are dealt to warps, that is in the order of additions.
     const int rep = nh / nkv;
     int hb = 1;
     for (int d = rep; d >= 1; --d)
-        if (rep % d == 0 && (long long)n_tokens * (nh / d) >= 2LL * st_sm_count()) { hb = d; break; }
+        if (rep % d == 0 && 4LL * n_tokens * (nh / d) >= 3LL * st_sm_count()) { hb = d; break; }
 #define GS_ARGS q, pool, c, out, items, positions, seq_of_token, slots, block_table, n_tokens, nh, hb, scale, mask, has_sink, \
                 sink, epi, status, s
     if (hb == 1) return launch_gqa_single<1>(GS_ARGS);
