@@ -361,10 +361,10 @@ delta_output_kernel(const float* __restrict__ o, const float* __restrict__ proj,
     }
 }
 
-// 0: the launcher chooses the lanes per column of the recurrence; 8, 16 or 32: this many (for tests and tuning).
+// 0: the launcher chooses the lanes per column of the recurrence; 8 or 16: this many (for tests and tuning).
 static int ds_forced_lanes = 0;
 ST_EXPORT int st_delta_rule_set_lanes(int lanes) {
-    if (lanes != 0 && lanes != 8 && lanes != 16 && lanes != 32) return ST_ERR_BAD_ARG;
+    if (lanes != 0 && lanes != 8 && lanes != 16) return ST_ERR_BAD_ARG;
     ds_forced_lanes = lanes;
     return 0;
 }
@@ -424,29 +424,25 @@ ST_EXPORT int st_delta_rule(const float* proj, int ld, int q_off, int b_off, int
                            (const float*)prep, sh, state, write_state, o, positions, q_start, slots);                \
     } while (0)
         // Lanes per column.  A token's step is a chain of dependent instructions, so a launch is as fast as its
-        // blocks are many: with few requests and heads, more lanes per column (fewer rows each, more stages of
-        // shuffles) spread the state over more multiprocessors.  Eight lanes once the blocks fill the device twice.
+        // blocks are spread: when eight lanes per column give fewer blocks than the device has multiprocessors,
+        // sixteen (fewer rows each, one more stage of shuffles) were measured faster, by a fifth for one request of
+        // eight heads; for short columns (dim <= 32) and for steps of many requests eight are.  Thirty-two lanes
+        // were measured too and never won.
         int lanes = ds_forced_lanes;
         if (!lanes) {
             const long long cols8 = (vd + DS_THREADS / 8 - 1) / (DS_THREADS / 8);
-            const long long blocks8 = (long long)n_seqs * H * cols8;
-            lanes = blocks8 >= 2 * st_sm_count() ? 8 : blocks8 * 2 >= 2 * st_sm_count() ? 16 : 32;
+            lanes = (dim > 32 && (long long)n_seqs * H * cols8 < st_sm_count()) ? 16 : 8;
         }
-        if (lanes == 8 && dim > 128) lanes = 16;
+        if (dim > 128) lanes = 16;
         if (lanes == 8) {
             if (dim <= 32) DS_LAUNCH(8, 4);
             else if (dim <= 64) DS_LAUNCH(8, 8);
             else DS_LAUNCH(8, 16);
-        } else if (lanes == 16) {
+        } else {
             if (dim <= 32) DS_LAUNCH(16, 2);
             else if (dim <= 64) DS_LAUNCH(16, 4);
             else if (dim <= 128) DS_LAUNCH(16, 8);
             else DS_LAUNCH(16, 16);
-        } else {
-            if (dim <= 32) DS_LAUNCH(32, 1);
-            else if (dim <= 64) DS_LAUNCH(32, 2);
-            else if (dim <= 128) DS_LAUNCH(32, 4);
-            else DS_LAUNCH(32, 8);
         }
 #undef DS_LAUNCH
         if (rc) return rc;

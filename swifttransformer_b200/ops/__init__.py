@@ -1181,7 +1181,7 @@ def delta_rule_scratch(n_tokens: int, H: int, G: int, dim: int, vd: int) -> int:
 
 
 def delta_rule_set_lanes(lanes: int) -> None:
-    """How many lanes share a column of the state in the recurrence: 8, 16 or 32, or 0 for the launcher's own choice by
+    """How many lanes share a column of the state in the recurrence: 8 or 16, or 0 for the launcher's own choice by
     the number of blocks a step gives (the default)."""
     _check(lib().st_delta_rule_set_lanes(int(lanes)), "delta_rule_set_lanes")
 

@@ -159,7 +159,7 @@ def test_delta_rule_in_portions_and_token_by_token(dtype, shape):
         assert err.max() < tol, (sizes, int(np.argmax(err > tol)), float(err.max()))
 
 
-@pytest.mark.parametrize("lanes", [8, 16, 32])
+@pytest.mark.parametrize("lanes", [8, 16])
 @pytest.mark.parametrize("shape", DELTA_SHAPES)
 def test_delta_rule_with_every_layout_of_the_state(lanes, shape):
     from swifttransformer_b200 import ops
