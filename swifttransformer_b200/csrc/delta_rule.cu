@@ -10,6 +10,10 @@
 //   S <- diag(decay) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 //   out      = out_scale * o / sqrt(mean(o^2) + eps) * w * sigmoid(sum_r g1_r * W_g2[h * vd + e, r])
 //
+// Two simpler forms of the same are taken by rank: with rank_a == 0 the projection holds one decay logit per head
+// at a_off (dt_bias is then [H] and all key channels of a head decay alike); with rank_g == 0 it holds the output
+// gate's logits themselves at g_off ([H * vd]).  gate_silu: the gate is z * sigmoid(z) instead of sigmoid(z).
+//
 // Three kernels.  delta_prepare turns a token's row of the float projection [q | k | v | b | a1 | g1] into a
 // float row [q (G*dim) | k (G*dim) | v (H*vd) | decay (H*dim) | beta (H)]; delta_scan walks each request's
 // tokens with the state's columns in registers (a column of S evolves on its own: its dot products with k and q
@@ -28,7 +32,8 @@
 struct DeltaShape {
     int H, G, dim, vd;            // value heads, query/key heads, key size, value size
     int q_off, k_off, v_off, b_off, a_off, g_off;   // columns of the projection
-    int rank_a, rank_g;
+    int rank_a, rank_g;           // 0: no low-rank pair, the projection holds the logits themselves (see below)
+    int gate_silu;                // the output gate: 0 sigmoid(z), 1 z * sigmoid(z)
     // columns of a prepared row
     __host__ __device__ int pq() const { return 0; }
     __host__ __device__ int pk() const { return G * dim; }
@@ -148,14 +153,21 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, DeltaShape sh, cons
     // decays: the low-rank step size, one thread per (head, key channel)
     __shared__ float xs_a[DR_RANK_SMEM];
     const float* xa = row + sh.a_off;
-    if (sh.rank_a <= DR_RANK_SMEM) {
+    if (sh.rank_a > 0 && sh.rank_a <= DR_RANK_SMEM) {
         for (int r = threadIdx.x; r < sh.rank_a; r += blockDim.x) xs_a[r] = __ldcg(xa + r);
         __syncthreads();
         xa = xs_a;
     }
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H * dim; c += blockDim.x * gridDim.y) {
-        const float z = lowrank_dot(xa, w_a2 + (size_t)c * sh.rank_a, sh.rank_a);
-        const float dt = softplusf_(z + dt_bias[c]);
+        float z, bias;
+        if (sh.rank_a > 0) {
+            z = lowrank_dot(xa, w_a2 + (size_t)c * sh.rank_a, sh.rank_a);
+            bias = dt_bias[c];
+        } else {
+            z = __ldcg(xa + c / dim);
+            bias = dt_bias[c / dim];
+        }
+        const float dt = softplusf_(z + bias);
         dst[sh.pd() + c] = expf(-expf(a_log[c / dim]) * dt);
     }
     if (!early) ST_PDL_TRIGGER();
@@ -350,14 +362,16 @@ delta_output_kernel(const float* __restrict__ o, const float* __restrict__ proj,
     const float inv = rsqrtf(ss / (float)vd + eps) * out_scale;
     __shared__ float xs_g[DR_RANK_SMEM];
     const float* g1 = proj + (size_t)t * ld + sh.g_off;
-    if (sh.rank_g <= DR_RANK_SMEM) {
+    if (sh.rank_g > 0 && sh.rank_g <= DR_RANK_SMEM) {
         for (int r = threadIdx.x; r < sh.rank_g; r += blockDim.x) xs_g[r] = __ldcg(g1 + r);
         __syncthreads();
         g1 = xs_g;
     }
     for (int e = threadIdx.x; e < vd; e += blockDim.x) {
-        const float z = lowrank_dot(g1, w_g2 + (size_t)(h * vd + e) * sh.rank_g, sh.rank_g);
-        out[((size_t)t * sh.H + h) * vd + e] = from_f32<T>(__ldcg(orow + e) * inv * norm_w[e] / (1.f + expf(-z)));
+        const float z = sh.rank_g > 0 ? lowrank_dot(g1, w_g2 + (size_t)(h * vd + e) * sh.rank_g, sh.rank_g)
+                                      : __ldcg(g1 + h * vd + e);
+        const float gate = (sh.gate_silu ? z : 1.f) / (1.f + expf(-z));
+        out[((size_t)t * sh.H + h) * vd + e] = from_f32<T>(__ldcg(orow + e) * inv * norm_w[e] * gate);
     }
 }
 
@@ -381,15 +395,15 @@ ST_EXPORT int st_delta_rule(const float* proj, int ld, int q_off, int b_off, int
                             float out_scale, float* state, int write_state, int single_tokens, float* scratch,
                             void* out, const int* positions, const int* seq_of_token, const int* q_start,
                             const int* slots, int n_tokens, int n_seqs, int H, int G, int dim, int vd, int dtype,
-                            void* stream) {
+                            void* stream, int gate_silu) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vd <= 0 || taps < 1 || rank_a <= 0 || rank_g <= 0) return ST_ERR_BAD_ARG;
+    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vd <= 0 || taps < 1 || rank_a < 0 || rank_g < 0) return ST_ERR_BAD_ARG;
     if (taps > DR_MAX_TAPS || dim > 32 * DR_UNIT_PASSES || vd > 32 * DR_UNIT_PASSES) return ST_ERR_TOO_LARGE;
     if (dtype != 0 && dtype != 1) return ST_ERR_BAD_DTYPE;
     DeltaShape sh;
     sh.H = H; sh.G = G; sh.dim = dim; sh.vd = vd;
     sh.q_off = q_off; sh.k_off = q_off + G * dim; sh.v_off = q_off + 2 * G * dim;
-    sh.b_off = b_off; sh.a_off = a_off; sh.g_off = g_off; sh.rank_a = rank_a; sh.rank_g = rank_g;
+    sh.b_off = b_off; sh.a_off = a_off; sh.g_off = g_off; sh.rank_a = rank_a; sh.rank_g = rank_g; sh.gate_silu = gate_silu;
     cudaStream_t s = (cudaStream_t)stream;
     float* prep = scratch;
     float* o = scratch + (size_t)n_tokens * sh.row();

@@ -68,12 +68,84 @@ gqa_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
     }
 }
 
+// The same with every query and key head divided by its root mean square over dim after the rotation
+// (x / sqrt(mean(x^2) + norm_eps), no weight): a warp per head, a lane holding dimensions lane, lane + 32, ...
+#define GP_NORM_PASSES 8      // heads of up to 32 * GP_NORM_PASSES dimensions
+template <typename T>
+__global__ void __launch_bounds__(GP_THREADS)
+gqa_prepare_norm_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+                        const float* __restrict__ bias, const float* __restrict__ inv_freq, int rot_dims,
+                        float temp_coef, int temp_every, float norm_eps, T* __restrict__ q_out, T* __restrict__ pool,
+                        DiffCache cache, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                        const int* __restrict__ slots, const int* __restrict__ block_table, int nh, int write_kv,
+                        int* __restrict__ status) {
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos < 0) return;
+    const int dim = cache.kd, vd = cache.vd, nkv = cache.nkv;
+    int page = -1;
+    if (write_kv) {
+        page = block_table[(size_t)slots[seq_of_token[t]] * cache.max_pages + pos / cache.page_size];
+        if (page < 0 && status && threadIdx.x == 0 && blockIdx.y == 0) *status = 1;
+    }
+    const int pip = pos % cache.page_size;
+    const int half = rot_dims / 2;
+    const float temp = temp_coef != 0.f ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
+    const T* row = proj + (size_t)t * ld;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = GP_THREADS / 32;
+    const int units = nh + (write_kv ? 2 * nkv : 0);            // query heads, key heads, value heads
+    for (int u = blockIdx.y * nwarp + warp; u < units; u += nwarp * gridDim.y) {
+        if (u >= nh && page < 0) continue;
+        if (u >= nh + nkv) {
+            const int head = u - nh - nkv;
+            for (int e = lane; e < vd; e += 32) {
+                const int col = v_off + head * vd + e;
+                cache_values(pool, cache, page, head, pip)[e] = from_f32<T>(load1_cg(row + col) + (bias ? bias[col] : 0.f));
+            }
+            continue;
+        }
+        const bool is_q = u < nh;
+        const int head = is_q ? u : u - nh;
+        const int col0 = (is_q ? q_off : k_off) + head * dim;
+        float x[GP_NORM_PASSES];
+        float ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < GP_NORM_PASSES; ++r) {
+            const int e = lane + 32 * r;
+            x[r] = 0.f;
+            if (e >= dim) continue;
+            const int col = col0 + e;
+            float v = load1_cg(row + col) + (bias ? bias[col] : 0.f);
+            if (e < rot_dims) {
+                const bool low = e < half;
+                const int pcol = low ? col + half : col - half;
+                const float y = load1_cg(row + pcol) + (bias ? bias[pcol] : 0.f);
+                float sn, cs;
+                sincosf((float)pos * inv_freq[low ? e : e - half], &sn, &cs);
+                v = low ? v * cs - y * sn : v * cs + y * sn;
+            }
+            x[r] = v;
+            ss = fmaf(v, v, ss);
+        }
+        const float mult = rsqrtf(warp_sum(ss) / (float)dim + norm_eps) * (is_q ? temp : 1.f);
+#pragma unroll
+        for (int r = 0; r < GP_NORM_PASSES; ++r) {
+            const int e = lane + 32 * r;
+            if (e >= dim) continue;
+            if (is_q) q_out[((size_t)t * nh + head) * dim + e] = from_f32<T>(x[r] * mult);
+            else cache_keys(pool, cache, page, head, pip)[e] = from_f32<T>(x[r] * mult);
+        }
+    }
+}
+
 ST_EXPORT int st_gqa_prepare(const void* proj, int ld, int q_off, int k_off, int v_off, const float* bias,
                              const float* inv_freq, int rot_dims, float temp_coef, int temp_every, void* q_out,
                              void* pool, long long page_stride, long long entry_offset, const int* positions,
                              const int* seq_of_token, const int* slots, const int* block_table, int max_pages,
                              int n_tokens, int nh, int nkv, int dim, int vd, int page_size, int write_kv, int* status,
-                             int dtype, void* stream) {
+                             int dtype, void* stream, float norm_eps) {
     if (n_tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || dim <= 0 || vd <= 0 || page_size <= 0) return ST_ERR_BAD_ARG;
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && !inv_freq)) return ST_ERR_BAD_ARG;
@@ -84,6 +156,24 @@ ST_EXPORT int st_gqa_prepare(const void* proj, int ld, int q_off, int k_off, int
     if (gy > 64) gy = 64;
     dim3 grid(n_tokens, gy);
     cudaStream_t s = (cudaStream_t)stream;
+    if (norm_eps > 0.f) {
+        if (dim > 32 * GP_NORM_PASSES) return ST_ERR_TOO_LARGE;
+        const int units = nh + (write_kv ? 2 * nkv : 0), per = GP_THREADS / 32;
+        int ny = (units + per - 1) / per;
+        if (ny > 64) ny = 64;
+        dim3 ngrid(n_tokens, ny);
+        if (dtype == 0)
+            return st_launch_pdl("gqa_prepare", gqa_prepare_norm_kernel<float>, ngrid, dim3(GP_THREADS), 0, s,
+                                 (const float*)proj, ld, q_off, k_off, v_off, bias, inv_freq, rot_dims, temp_coef,
+                                 temp_every, norm_eps, (float*)q_out, (float*)pool, c, positions, seq_of_token, slots,
+                                 block_table, nh, write_kv, status);
+        if (dtype == 1)
+            return st_launch_pdl("gqa_prepare", gqa_prepare_norm_kernel<bf16>, ngrid, dim3(GP_THREADS), 0, s,
+                                 (const bf16*)proj, ld, q_off, k_off, v_off, bias, inv_freq, rot_dims, temp_coef,
+                                 temp_every, norm_eps, (bf16*)q_out, (bf16*)pool, c, positions, seq_of_token, slots,
+                                 block_table, nh, write_kv, status);
+        return ST_ERR_BAD_DTYPE;
+    }
     if (dtype == 0)
         return st_launch_pdl("gqa_prepare", gqa_prepare_kernel<float>, grid, dim3(GP_THREADS), 0, s, (const float*)proj, ld,
                              q_off, k_off, v_off, bias, inv_freq, rot_dims, temp_coef, temp_every, (float*)q_out,
@@ -170,6 +260,7 @@ gqa_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, 
         __syncthreads();
     }
     if (has_sink) {
+        if (epi.sinks) sink = epi.sinks[h];
         const float n = fmaxf(m, sink);
         const float corr = m == -INFINITY ? 0.f : expf(m - n);
         l = l * corr + expf(sink - n);
@@ -193,13 +284,13 @@ ST_EXPORT int st_gqa_attention_plain(const void* q, const void* pool, long long 
                                      const int* slots, const int* block_table, int max_pages, int n_tokens, int nh,
                                      int nkv, int dim, int vd, int page_size, float scale, int window, int keep_first,
                                      int has_sink, float sink, const void* gate, long long gate_ld, float out_scale,
-                                     int* status, int dtype, void* stream) {
+                                     int* status, int dtype, void* stream, const float* sinks) {
     if (n_tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || dim <= 0 || vd <= 0 || page_size <= 0 || keep_first < 0) return ST_ERR_BAD_ARG;
     if (vd > G_VPASS * GK || dim > 4096) return ST_ERR_TOO_LARGE;
     const DiffCache c = {max_pages, page_size, nkv, dim, vd, page_stride, entry_offset};
     const GqaMask mask = {window, keep_first};
-    const GqaEpilogue epi = {gate, gate_ld, out_scale};
+    const GqaEpilogue epi = {gate, gate_ld, out_scale, has_sink ? sinks : nullptr};
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, nh);
     const size_t smem = (size_t)(dim + GK) * sizeof(float);
@@ -432,14 +523,15 @@ gqa_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             L += sl[w * REP + r];
             O += so[((size_t)w * REP + r) * vd + e];
         }
+        const int h = h0 + r;
         if (has_sink) {
-            const float n = fmaxf(mr, sink);
+            const float sk = epi.sinks ? epi.sinks[h] : sink;
+            const float n = fmaxf(mr, sk);
             const float c = mr == -INFINITY ? 0.f : expf(mr - n);
-            L = fmaf(L, c, expf(sink - n));
+            L = fmaf(L, c, expf(sk - n));
             O *= c;
         }
         float o = L > 0.f ? O * epi.out_scale / L : 0.f;
-        const int h = h0 + r;
         if (gate) o *= sigmoidf_(load1_cg(gate + (size_t)t * epi.gate_ld + h * vd + e));
         out[((size_t)t * nh + h) * vd + e] = __float2bfloat16_rn(o);
     }
@@ -478,13 +570,13 @@ ST_EXPORT int st_gqa_attention_single(const void* q, const void* pool, long long
                                       const int* slots, const int* block_table, int max_pages, int n_tokens, int nh,
                                       int nkv, int dim, int vd, int page_size, float scale, int window, int keep_first,
                                       int has_sink, float sink, const void* gate, long long gate_ld, float out_scale,
-                                      int* status, void* stream) {
+                                      int* status, void* stream, const float* sinks) {
     if (n_tokens <= 0) return 0;
     if (page_size <= 0 || keep_first < 0) return ST_ERR_BAD_ARG;
     if (!st_gqa_attention_single_applies(nh, nkv, dim, vd)) return ST_ERR_BAD_SIZE;
     const DiffCache c = {max_pages, page_size, nkv, dim, vd, page_stride, entry_offset};
     const GqaMask mask = {window, keep_first};
-    const GqaEpilogue epi = {gate, gate_ld, out_scale};
+    const GqaEpilogue epi = {gate, gate_ld, out_scale, has_sink ? sinks : nullptr};
     cudaStream_t s = (cudaStream_t)stream;
     // Query heads per block: the whole group when that gives blocks for three quarters of the device (a key or value
     // row is then fetched once for the group), else the largest part of the group that does, down to one head; the

@@ -26,10 +26,12 @@ __device__ __forceinline__ bool gqa_seen(int key, int pos, const GqaMask& m) {
 
 // What is done to a head's result before it is stored: times out_scale, and, with gate, times
 // sigmoid(gate[token * gate_ld + head * vd + e]) (gate logits as a product left them, in the storage type).
+// sinks: with has_sink, the extra term's logit of every head (float [heads]); null: the one `sink` for all heads.
 struct GqaEpilogue {
     const void* gate;
     long long gate_ld;
     float out_scale;
+    const float* sinks;
 };
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }

@@ -246,7 +246,7 @@ gqa_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
     for (int r = 0; r < 2; ++r) {
         float ll = l[r], c = 1.f;
         if (has_sink) {
-            const float s_l2 = sink * LOG2E;
+            const float s_l2 = (epi.sinks ? epi.sinks[h] : sink) * LOG2E;
             const float m_new = fmaxf(m[r], s_l2);
             c = m[r] == -INFINITY ? 0.f : fast_exp2(m[r] - m_new);
             ll = ll * c + fast_exp2(s_l2 - m_new);
@@ -306,14 +306,14 @@ ST_EXPORT int st_gqa_attention_tiles(const void* q, const void* pool, long long 
                                      const int* start_pos, const int* slots, const int* block_table, int max_pages,
                                      int nh, int nkv, int dim, int vd, int page_size, float scale, int window,
                                      int keep_first, int has_sink, float sink, const void* gate, long long gate_ld,
-                                     float out_scale, int* status, void* stream) {
+                                     float out_scale, int* status, void* stream, const float* sinks) {
     if (n_tiles <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || tile_rows <= 0 || keep_first < 0) return ST_ERR_BAD_ARG;
     if (!st_gqa_attention_tiles_applies(dim, vd)) return ST_ERR_BAD_SIZE;
     if (gate && ((gate_ld & 1) || ((uintptr_t)gate & 3))) return ST_ERR_BAD_ARG;
     const DiffCache c = {max_pages, page_size, nkv, dim, vd, page_stride, entry_offset};
     const GqaMask mask = {window, keep_first};
-    const GqaEpilogue epi = {gate, gate_ld, out_scale};
+    const GqaEpilogue epi = {gate, gate_ld, out_scale, has_sink ? sinks : nullptr};
     cudaStream_t s = (cudaStream_t)stream;
 #define GT_ARGS q, pool, c, out, tiles, n_tiles, tile_rows, q_start, start_pos, slots, block_table, nh, scale, mask, has_sink, \
                 sink, epi, status, s

@@ -2,7 +2,7 @@
 // sum of the experts' results.
 //
 // moe_route:   z = W_r h (float, W_r float [experts, width]); s = softmax(z) over all experts; the `top` experts
-//              with the largest s (ties: the lower index) and their s as weights (not renormalised, unless asked);
+//              with the largest s (ties: the lower index) and their s as weights (not renormalised, unless asked: then divided by their sum + 1e-20);
 //              optionally g = sigmoid(w_g . h), one number per token (the gate of a shared expert).
 //              A padding token (position < 0) gets expert -1.
 // moe_sort:    the step's (token, choice) items grouped by expert: offsets[e]..offsets[e+1] are expert e's places
@@ -83,7 +83,7 @@ moe_route_kernel(const T* __restrict__ h, int width, const float* __restrict__ w
         __syncwarp();
     }
     if (renorm && lane == 0)
-        for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] /= chosen_sum;
+        for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] /= chosen_sum + 1e-20f;
 }
 
 ST_EXPORT int st_moe_route(const void* h, int n_tokens, int width, const float* w_r, int n_experts, int top, int renorm,

@@ -84,6 +84,13 @@ class ModelDef:
     def num_cache_entries(self) -> int:
         return 1 + max((s.cache for s in self.layer_order), default=-1)
 
+    def _block_need(self, index: int) -> Any:
+        """What a block keeps per request: its own ``cache_spec()`` when it has one (a block with state beside its
+        mixer's), else its mixer's."""
+        block = self.blocks[index]
+        own = getattr(block, "cache_spec", None)
+        return own() if own is not None else block.mixer.cache_spec()
+
     def cache_specs(self) -> List[Any]:
         """The cache need of every cache entry (PagedKVSpec, StateSpec or None), by entry index."""
         specs: List[Any] = [None] * self.num_cache_entries()
@@ -93,7 +100,7 @@ class ModelDef:
                 if self.blocks[st.block].mixer is not None:
                     raise ValueError("a layer step without a cache entry runs a block with a mixer")
                 continue
-            spec = self.blocks[st.block].mixer.cache_spec()
+            spec = self._block_need(st.block)
             if st.writes_cache:
                 if owner[st.cache]:
                     raise ValueError(f"cache entry {st.cache} is written by two layer steps")
@@ -101,7 +108,7 @@ class ModelDef:
                 specs[st.cache] = spec
         for st in self.layer_order:
             if not st.writes_cache and st.cache >= 0:
-                spec = self.blocks[st.block].mixer.cache_spec()
+                spec = self._block_need(st.block)
                 if not owner[st.cache]:
                     raise ValueError(f"cache entry {st.cache} is read but no layer step writes it")
                 if spec != specs[st.cache]:
@@ -166,11 +173,13 @@ class CausalLM:
             stream.turn = st.turn
             self.blocks[st.block].forward(stream, ctx, caches[st.cache].view(st.writes_cache) if st.cache >= 0 else None)
             if self.after_layer is not None:
+                stream.fold()
                 self.after_layer(i, stream)
             if nvtx:
                 torch.cuda.nvtx.range_pop()
         if ctx.n_want == 0:
             return None
+        stream.fold()
         if self.final_norm is not None:
             h = self.final_norm.apply(stream.x, stream.pending, act_dtype=self.dtype, rows=ctx.want_rows)
         else:

@@ -1126,12 +1126,14 @@ def gqa_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bias: Op
                 inv_freq: Optional[torch.Tensor], rot_dims: int, temp_coef: float, temp_every: int,
                 q_out: torch.Tensor, pool: torch.Tensor, layer: int, positions: torch.Tensor,
                 seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int,
-                dim: int, vd: int, page_size: int, status: Optional[torch.Tensor], write_kv: bool = True) -> None:
+                dim: int, vd: int, page_size: int, status: Optional[torch.Tensor], write_kv: bool = True,
+                norm_eps: float = 0.0) -> None:
     """Queries, keys and values of a step from the fused projection ``proj`` [tokens, columns] (queries at column
     q_off, keys at k_off, values at v_off): plus ``bias`` (float32, one number per column of proj, or None); the
     first ``rot_dims`` dimensions of every query and key head rotated by position in the halves layout; queries
     times 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1); queries to ``q_out`` [tokens, nh * dim], keys and
-    values into their pages (``write_kv`` False: queries only)."""
+    values into their pages (``write_kv`` False: queries only).  ``norm_eps`` > 0: after the rotation every query and
+    key head is divided by its root mean square over ``dim`` (eps inside the root, no weight)."""
     assert proj.is_contiguous() and q_out.is_contiguous() and q_out.shape == (proj.shape[0], nh * dim)
     assert proj.dtype == q_out.dtype == pool.dtype
     if bias is not None:
@@ -1140,7 +1142,18 @@ def gqa_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bias: Op
     _check(lib().st_gqa_prepare(_p(proj), proj.shape[1], q_off, k_off, v_off, _p(bias), _p(inv_freq), rot_dims,
                                 _f(temp_coef), temp_every, _p(q_out), _p(pool), stride, off, _p(positions),
                                 _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1], proj.shape[0], nh,
-                                nkv, dim, vd, page_size, int(write_kv), _p(status), _dt(proj), _stream()), "gqa_prepare")
+                                nkv, dim, vd, page_size, int(write_kv), _p(status), _dt(proj), _stream(),
+                                _f(norm_eps)), "gqa_prepare")
+
+
+def _sink_args(sink, nh: int):
+    """(has_sink, the one logit, the logits per head): ``sink`` is None, a number, or a float32 tensor [heads]."""
+    if sink is None:
+        return 0, _f(0.0), None
+    if isinstance(sink, torch.Tensor):
+        assert sink.dtype == torch.float32 and sink.numel() == nh and sink.is_contiguous()
+        return 1, _f(0.0), _p(sink)
+    return 1, _f(float(sink)), None
 
 
 def _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink, gate, gate_off, out_scale):
@@ -1161,16 +1174,18 @@ def gqa_attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: to
     """Grouped attention of every token of the step (or of those ``items`` lists) over the paged cache, in float
     arithmetic for either storage type.  ``window`` 0: all keys up to the query; else the last ``window`` keys and
     the request's first ``keep_first``.  ``sink``: a logit that joins the softmax's denominator (None: none).
-    ``gate`` [tokens, columns]: the head's result is multiplied by sigmoid of its columns from ``gate_off`` on."""
+    ``gate`` [tokens, columns]: the head's result is multiplied by sigmoid of its columns from ``gate_off`` on.
+    ``sink`` may also be a float32 tensor [heads]: a logit per head."""
     assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
     stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink,
                                                gate, gate_off, out_scale)
     n = q.shape[0] if items is None else (n_items if n_items is not None else items.numel())
+    has_sink, sink_one, sinks = _sink_args(sink, nh)
     _check(lib().st_gqa_attention_plain(_p(q), _p(pool), stride, off, _p(out), _p(items), _p(positions),
                                         _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1], n, nh, nkv,
-                                        dim, vd, page_size, _f(scale), window, keep_first, int(sink is not None),
-                                        _f(sink or 0.0), gate_ptr, gate_ld, _f(out_scale), _p(status), _dt(q),
-                                        _stream()), "gqa_attention_plain")
+                                        dim, vd, page_size, _f(scale), window, keep_first, has_sink,
+                                        sink_one, gate_ptr, gate_ld, _f(out_scale), _p(status), _dt(q),
+                                        _stream(), sinks), "gqa_attention_plain")
     return out
 
 
@@ -1190,27 +1205,33 @@ def delta_rule(proj: torch.Tensor, b_off: int, a_off: int, g_off: int, conv_w: t
                w_a2: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, w_g2: torch.Tensor, norm_w: torch.Tensor,
                eps: float, out_scale: float, state: torch.Tensor, write_state: bool, single_tokens: bool,
                scratch: torch.Tensor, out: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
-               q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, H: int, G: int, dim: int, vd: int) -> torch.Tensor:
+               q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, H: int, G: int, dim: int, vd: int,
+               gate_silu: bool = False) -> torch.Tensor:
     """The gated delta rule over each request's tokens of the step, from the float32 projection ``proj`` [tokens,
     columns] = q (G * dim) | k (G * dim) | v (H * vd) from column 0, write strengths at b_off (H), the low-rank
     inputs of the decays at a_off and of the output gates at g_off.  ``conv_w`` float32 [channels, taps], the
     filters of q | k | v; ``conv_state`` float32 [slots, taps - 1, channels] is read and, when every request brings
     one token, moved on (else ``conv_state_update`` follows); ``state`` float32 [slots, H, dim, vd] is read and
-    moved on.  out [tokens, H * vd] in the type of ``w_a2`` / ``w_g2``."""
+    moved on.  out [tokens, H * vd] in the type of ``w_a2`` / ``w_g2``.  ``w_a2`` None: the projection holds one
+    decay logit per head at a_off and ``dt_bias`` is [H]; ``w_g2`` None: it holds the output gate's H * vd logits
+    at g_off.  ``gate_silu``: the gate is z * sigmoid(z) instead of sigmoid(z)."""
     assert proj.dtype == torch.float32 and proj.is_contiguous() and out.is_contiguous()
-    assert out.shape == (proj.shape[0], H * vd) and w_a2.dtype == w_g2.dtype == out.dtype
+    assert out.shape == (proj.shape[0], H * vd) and all(w is None or w.dtype == out.dtype for w in (w_a2, w_g2))
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dim, vd)
     channels = 2 * G * dim + H * vd
     taps = conv_w.shape[1]
     assert conv_w.dtype == torch.float32 and conv_w.shape[0] == channels and conv_w.is_contiguous()
     assert conv_state.dtype == torch.float32 and conv_state.shape[1:] == (taps - 1, channels)
-    assert w_a2.is_contiguous() and w_g2.is_contiguous() and w_a2.shape[0] == H * dim and w_g2.shape[0] == H * vd
+    assert w_a2 is None or (w_a2.is_contiguous() and w_a2.shape[0] == H * dim)
+    assert w_g2 is None or (w_g2.is_contiguous() and w_g2.shape[0] == H * vd)
+    assert dt_bias.numel() == (H * dim if w_a2 is not None else H)
     assert scratch.dtype == torch.float32 and scratch.numel() >= delta_rule_scratch(proj.shape[0], H, G, dim, vd)
-    _check(lib().st_delta_rule(_p(proj), proj.shape[1], 0, b_off, a_off, g_off, w_a2.shape[1], w_g2.shape[1],
+    _check(lib().st_delta_rule(_p(proj), proj.shape[1], 0, b_off, a_off, g_off,
+                               w_a2.shape[1] if w_a2 is not None else 0, w_g2.shape[1] if w_g2 is not None else 0,
                                _p(conv_w), taps, _p(conv_state), _p(w_a2), _p(a_log), _p(dt_bias), _p(w_g2),
                                _p(norm_w), _f(eps), _f(out_scale), _p(state), int(write_state), int(single_tokens),
                                _p(scratch), _p(out), _p(positions), _p(seq_of_token), _p(q_start), _p(slots),
-                               proj.shape[0], n_seqs, H, G, dim, vd, _dt(out), _stream()), "delta_rule")
+                               proj.shape[0], n_seqs, H, G, dim, vd, _dt(out), _stream(), int(gate_silu)), "delta_rule")
     return out
 
 
@@ -1247,11 +1268,12 @@ def gqa_attention_tiles(q: torch.Tensor, pool: torch.Tensor, layer: int, out: to
     assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
     stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink,
                                                gate, gate_off, out_scale)
+    has_sink, sink_one, sinks = _sink_args(sink, nh)
     _check(lib().st_gqa_attention_tiles(_p(q), _p(pool), stride, off, _p(out), _p(tiles), n_tiles, tile_rows,
                                         _p(q_start), _p(start_pos), _p(slots), _p(block_table), block_table.shape[1],
                                         nh, nkv, dim, vd, page_size, _f(scale), window, keep_first,
-                                        int(sink is not None), _f(sink or 0.0), gate_ptr, gate_ld, _f(out_scale),
-                                        _p(status), _stream()), "gqa_attention_tiles")
+                                        has_sink, sink_one, gate_ptr, gate_ld, _f(out_scale),
+                                        _p(status), _stream(), sinks), "gqa_attention_tiles")
     return out
 
 
@@ -1270,9 +1292,106 @@ def gqa_attention_single(q: torch.Tensor, pool: torch.Tensor, layer: int, out: t
     stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, sink,
                                                gate, gate_off, out_scale)
     n = q.shape[0] if items is None else (n_items if n_items is not None else items.numel())
+    has_sink, sink_one, sinks = _sink_args(sink, nh)
     _check(lib().st_gqa_attention_single(_p(q), _p(pool), stride, off, _p(out), _p(items), _p(positions),
                                          _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1], n, nh, nkv,
-                                         dim, vd, page_size, _f(scale), window, keep_first, int(sink is not None),
-                                         _f(sink or 0.0), gate_ptr, gate_ld, _f(out_scale), _p(status), _stream()),
+                                         dim, vd, page_size, _f(scale), window, keep_first, has_sink,
+                                         sink_one, gate_ptr, gate_ld, _f(out_scale), _p(status), _stream(), sinks),
            "gqa_attention_single")
     return out
+
+
+# ------------------------------------------------------------ several residual streams, paired norms, xIELU
+def hc_spread(x: torch.Tensor, n_streams: int) -> torch.Tensor:
+    """n copies of the float32 rows x [tokens, width] -> lanes [n, tokens, width]."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    lanes = torch.empty((n_streams,) + tuple(x.shape), dtype=torch.float32, device=x.device)
+    _check(lib().st_hc_spread(_p(x), _p(lanes), ctypes.c_longlong(x.numel()), n_streams, _stream()), "hc_spread")
+    return lanes
+
+
+def hc_sum(lanes: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The sum of the streams, lanes [n, tokens, width] float32 -> [tokens, width]."""
+    assert lanes.dtype == torch.float32 and lanes.is_contiguous() and lanes.dim() == 3
+    if out is None:
+        out = torch.empty(lanes.shape[1:], dtype=torch.float32, device=lanes.device)
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == lanes.shape[1:]
+    _check(lib().st_hc_sum(_p(lanes), _p(out), ctypes.c_longlong(out.numel()), lanes.shape[0], _stream()), "hc_sum")
+    return out
+
+
+def hc_read_norm(lanes: torch.Tensor, coef: torch.Tensor, gain: torch.Tensor, eps: float,
+                 positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """u = sum_s coef[s] * lanes[s]; -> u / sqrt(mean(u^2) + eps) * gain, float32 [tokens, width]."""
+    n, tokens, width = lanes.shape
+    assert lanes.dtype == torch.float32 and lanes.is_contiguous()
+    assert coef.dtype == torch.float32 and coef.numel() == n and gain.dtype == torch.float32 and gain.numel() == width
+    out = torch.empty((tokens, width), dtype=torch.float32, device=lanes.device)
+    _check(lib().st_hc_read_norm(_p(lanes), n, _p(coef), _p(gain), _f(eps), tokens, width, _p(out), _p(positions),
+                                 _stream()), "hc_read_norm")
+    return out
+
+
+def hc_write(lanes: torch.Tensor, mix: torch.Tensor, out_coef: torch.Tensor, y: torch.Tensor) -> None:
+    """lanes[t] <- sum_s mix[s, t] * lanes[s] + out_coef[t] * y, all t at once from the old lanes, in place."""
+    n, tokens, width = lanes.shape
+    assert lanes.dtype == torch.float32 and lanes.is_contiguous() and y.is_contiguous() and y.shape == (tokens, width)
+    assert mix.dtype == torch.float32 and mix.shape == (n, n) and mix.is_contiguous()
+    assert out_coef.dtype == torch.float32 and out_coef.numel() == n
+    _check(lib().st_hc_write(_p(lanes), n, _p(mix), _p(out_coef), _p(y), _dt(y), tokens, width, _stream()), "hc_write")
+
+
+def norm_pair_sum(a: torch.Tensor, wa: torch.Tensor, ca: float, b: torch.Tensor, wb: torch.Tensor, cb: float,
+                  eps: float, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """ca * wa * a / rms(a) + cb * wb * b / rms(b) row by row (rms over the row, eps inside the root), float32."""
+    assert a.is_contiguous() and b.is_contiguous() and a.shape == b.shape and a.dim() == 2
+    assert wa.dtype == wb.dtype == torch.float32 and wa.numel() == wb.numel() == a.shape[1]
+    out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+    _check(lib().st_norm_pair_sum(_p(a), _dt(a), _p(wa), _f(ca), _p(b), _dt(b), _p(wb), _f(cb), _f(eps), a.shape[0],
+                                  a.shape[1], _p(out), _p(positions), _stream()), "norm_pair_sum")
+    return out
+
+
+def xielu(z: torch.Tensor, alpha_pos: float, alpha_neg: float, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """z > 0: alpha_pos * z^2 + z / 2;  z <= 0: alpha_neg * (exp(z) - 1 - z) + z / 2.  z float32 or the storage type."""
+    assert z.is_contiguous()
+    out_dtype = out_dtype or z.dtype
+    assert z.dtype in (torch.float32, out_dtype)
+    out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+    _check(lib().st_xielu(_p(z), int(z.dtype == torch.float32), _p(out), ctypes.c_longlong(z.numel()), _f(alpha_pos),
+                          _f(alpha_neg), _dt(out), _stream()), "xielu")
+    return out
+
+
+# ------------------------------------------------------------ attention whose weights are mixed over heads
+def talk_attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
+                         seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int,
+                         dim: int, vd: int, page_size: int, scale: float, window: int, keep_first: int,
+                         talk: Optional[torch.Tensor], sinks: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                         gate_off: int, gate_heads: bool, out_scale: float, status: Optional[torch.Tensor] = None,
+                         items: Optional[torch.Tensor] = None, n_items: Optional[int] = None) -> torch.Tensor:
+    """Grouped attention over the paged cache whose normalised softmax weights are mixed over the heads before they
+    meet the values: P'_a = sum_b talk[a, b] P_b, head a applying P'_a to the values of its own key/value head.
+    ``talk`` float32 [heads, heads] (None: the identity); ``sinks`` float32 [heads]: a logit per head in the
+    denominator (None: none); ``gate`` [tokens, columns]: sigmoid of its columns from ``gate_off`` on, one per head
+    (``gate_heads``) or one per (head, value dimension).  Float arithmetic for either storage type."""
+    assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
+    stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, None,
+                                               gate, gate_off, out_scale)
+    if talk is not None:
+        assert talk.dtype == torch.float32 and talk.shape == (nh, nh) and talk.is_contiguous()
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.numel() == nh and sinks.is_contiguous()
+    n = q.shape[0] if items is None else (n_items if n_items is not None else items.numel())
+    _check(lib().st_talk_attention_plain(_p(q), _p(pool), stride, off, _p(out), _p(items), _p(positions),
+                                         _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1], n, nh, nkv,
+                                         dim, vd, page_size, _f(scale), window, keep_first, _p(talk), _p(sinks),
+                                         gate_ptr, gate_ld, int(gate_heads), _f(out_scale), _p(status), _dt(q),
+                                         _stream()), "talk_attention_plain")
+    return out
+
+
+def talk_attention_tiles_applies(q: torch.Tensor, nh: int, nkv: int, dim: int, vd: int) -> bool:
+    """Whether the tensor-core kernel for query tiles takes these sizes (bfloat16 only)."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and hasattr(lib(), "st_talk_attention_tiles_applies")
+            and bool(lib().st_talk_attention_tiles_applies(nh, nkv, dim, vd)))

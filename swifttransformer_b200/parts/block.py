@@ -11,6 +11,9 @@ parallel  (one norm, both sub-layers read its output):
     h = norm1(x);  x' = x + (mixer(h) + ffn(h))
 reentry   (no sub-layers; opens a pass over a stretch of layers that runs several times):
     x' = W [x ; x0] + step[turn]         x0: the embedding's rows, turn: the number of the pass
+hyper_pre_norm (n copies x_1..x_n of the residual rows instead of one; sub-layer f with coefficients a, b, M):
+    u = sum_s a_s x_s;  y = f(c(norm(u)));  x_t' = sum_s M[s, t] x_s + b_t y        c: an optional short
+    convolution over time, c(h) = h + conv(h); the model's residual rows are the sum of the copies
 
 The residual stream is float32 for every storage type.  A block leaves the
 feed-forward's result as ``pending``: the next norm kernel (of the next block
@@ -36,6 +39,14 @@ class ResidualStream:
     act: Optional[torch.Tensor] = None     # x in the activation dtype, when current
     x0: Optional[torch.Tensor] = None      # the embedding's rows in the activation dtype (models that ask for them)
     turn: int = 0                          # which pass over a stretch of shared layers the running step belongs to
+    lanes: Optional[torch.Tensor] = None   # [n, N, width] float32: the copies of a model with several residual streams
+
+    def fold(self) -> None:
+        """A model with several residual streams: x <- their sum (what the final norm and the tools that look at
+        the residual rows read); the copies themselves stay as they are."""
+        if self.lanes is not None:
+            ops.hc_sum(self.lanes, out=self.x)
+            self.pending, self.act = None, None
 
     def materialise(self, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x + pending in the activation dtype (all rows, folding pending into x; or only ``rows``)."""
@@ -223,3 +234,103 @@ class ReentryBlock(Block):
         both = ops.concat_rows(stream.materialise(), stream.x0)
         stream.x = ops.linear(both, self.w_in, out_dtype=torch.float32)
         stream.pending, stream.act = Delta(None, self.step[stream.turn]), None
+
+
+@BLOCKS.register("hyper_pre_norm")
+class HyperPreNormBlock(Block):
+    """A pre-norm block over ``streams`` copies of the residual rows ("hyper-connections").  For each of its two
+    sub-layers (the mixer, then the feed-forward, which may be absent) with the tensors ``<hc>.in`` [n], ``<hc>.out``
+    [n] and ``<hc>.mix`` [n, n] (indexed [from, to]):
+
+        u = sum_s in[s] x_s;   h = norm(u);   h <- h + conv(h) (``canon_names``: a filter [width, taps] per
+        sub-layer, or None);   y = sub-layer(h);   x_t <- sum_s mix[s, t] x_s + out[t] y   for all t at once.
+
+    The copies start as the embedding's rows (made by the first block that runs) and ``ResidualStream.fold`` sums
+    them.  Mixture, norm statistics, the convolution and the update are float arithmetic on float rows; the
+    sub-layers get h in the activation type.  Per request the block keeps the convolutions' last taps - 1 inputs in
+    state slots of its own beside the mixer's cache: its cache entry is (state 1, the mixer's need, state 2)."""
+
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], norm1: Norm, norm2: Optional[Norm],
+                 streams: int, width: int, hc_names: tuple, canon_names: Optional[tuple] = None, taps: int = 1):
+        if (feed_forward is None) != (norm2 is None):
+            raise ValueError("a block has a second norm exactly when it has a feed-forward")
+        if streams < 1:
+            raise ValueError("a model has at least one residual stream")
+        if canon_names is not None and taps < 1:
+            raise ValueError("a convolution needs at least one tap")
+        super().__init__(mixer, feed_forward, norm1, norm2)
+        self.streams, self.width, self.taps = int(streams), int(width), int(taps)
+        self.hc_names, self.canon_names = tuple(hc_names), (tuple(canon_names) if canon_names else None)
+        self.n_sub = 1 if feed_forward is None else 2
+        self.coef = [None, None]
+        self.filters = [None, None]
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def param_specs(self):
+        from ..weights.spec import VECTOR, ParamSpec
+        n, specs = self.streams, []
+        for i in range(self.n_sub):
+            hc = self.hc_names[i]
+            specs += [ParamSpec(hc + ".in", (n,), VECTOR), ParamSpec(hc + ".out", (n,), VECTOR),
+                      ParamSpec(hc + ".mix", (n, n), VECTOR)]
+            if self.canon_names is not None:
+                specs.append(ParamSpec(self.canon_names[i], (self.width, self.taps), VECTOR))
+        return specs
+
+    def bind(self, tensors) -> None:
+        for i in range(self.n_sub):
+            hc = self.hc_names[i]
+            self.coef[i] = tuple(tensors[hc + k].to(torch.float32).contiguous() for k in (".in", ".mix", ".out"))
+            if self.canon_names is not None:
+                self.filters[i] = tensors[self.canon_names[i]].to(torch.float32).contiguous()
+
+    def param_bytes(self) -> int:
+        return 4 * self.n_sub * (self.width * self.taps if self.canon_names is not None else 0)
+
+    def cache_spec(self):
+        from .base import StateSpec
+        tail = StateSpec((self.taps - 1, self.width), torch.float32) \
+            if self.canon_names is not None and self.taps > 1 else None
+        return (tail, self.mixer.cache_spec(), tail if self.n_sub == 2 else None)
+
+    def _input(self, i: int, stream: ResidualStream, norm: Norm, ctx: Any, tail: Any) -> torch.Tensor:
+        a, _, _ = self.coef[i]
+        h = ops.hc_read_norm(stream.lanes, a, norm.gamma, norm.eps, ctx.positions)
+        out = torch.empty(h.shape, dtype=stream.act_dtype, device=h.device)
+        if self.canon_names is None:
+            if stream.act_dtype == torch.float32:
+                return h
+            ops.add_norm(h, kind="none", out_act=out)
+            return out
+        state = tail.state if tail is not None else h.new_zeros((1, 0, self.width))
+        ops.conv_residual(h, self.filters[i], state, out, ctx.positions, ctx.seq_of_token, ctx.q_start, ctx.slots)
+        return out
+
+    @staticmethod
+    def _rows(delta: Delta, stream: ResidualStream) -> torch.Tensor:
+        """What a sub-layer left, as one tensor of rows (float or the activation type)."""
+        if delta.bias is None and delta.parts is None:
+            return delta.value
+        if delta.bias is None and delta.value is None and delta.parts.shape[0] == 1:
+            return delta.parts[0]
+        y = torch.zeros(stream.x.shape, dtype=torch.float32, device=stream.x.device)
+        ops.add_norm(y, delta=delta.value, delta_bias=delta.bias, parts=delta.parts, resid_out=y, kind="none",
+                     act_dtype=stream.act_dtype)
+        return y
+
+    def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
+        if stream.lanes is None:
+            if stream.pending is not None:
+                stream.materialise()
+            stream.lanes = ops.hc_spread(stream.x, self.streams)
+        tail1, mixer_cache, tail2 = cache
+        h = self._input(0, stream, self.norm1, ctx, tail1)
+        y = self._rows(self.mixer.forward(h, ctx, mixer_cache), stream)
+        ops.hc_write(stream.lanes, self.coef[0][1], self.coef[0][2], y)
+        if self.feed_forward is not None:
+            h = self._input(1, stream, self.norm2, ctx, tail2)
+            y = self._rows(self.feed_forward.forward(h, ctx), stream)
+            ops.hc_write(stream.lanes, self.coef[1][1], self.coef[1][2], y)
+        stream.pending, stream.act = None, None

@@ -15,6 +15,10 @@ the q | k | v projection and the matrices S_a, both float32, in state slots.  On
 q | k | v | b | W_a1 h | W_g1 h in float32 (what enters the recurrence stays float from the accumulator on); the
 two low-rank expansions, the gates, the norms and the recurrence are float arithmetic in the kernels.  The ranks
 of the low-rank pairs are read from the tensors.
+
+``low_rank`` False gives the plainer form of the same mixer: one decay per head and token,
+decay_a = exp(-exp(A_log_a) * softplus((W_a h)_a + dt_bias_a)) with W_a [heads, hidden] and dt_bias [heads], and an
+output gate from a full projection W_g [heads * vdim, hidden]; ``gate_act`` "silu" makes the gate z * sigmoid(z).
 """
 from __future__ import annotations
 
@@ -34,11 +38,15 @@ class GatedDeltaRule(Mixer):
     low-rank pairs' inner size when weights are made at random (a checkpoint's own is taken as it is)."""
 
     def __init__(self, hidden: int, num_heads: int, num_qk_heads: int, dim: int, vdim: int, conv_taps: int, eps: float,
-                 names: Dict[str, str], out_scale: float = 1.0, float_out: bool = False, rank: int = 16):
+                 names: Dict[str, str], out_scale: float = 1.0, float_out: bool = False, rank: int = 16,
+                 low_rank: bool = True, gate_act: str = "sigmoid"):
         if num_heads % num_qk_heads:
             raise ValueError(f"{num_heads} value heads cannot share {num_qk_heads} query/key heads")
         if conv_taps < 1:
             raise ValueError("a convolution needs at least one tap")
+        if gate_act not in ("sigmoid", "silu"):
+            raise ValueError("the output gate is 'sigmoid' or 'silu'")
+        self.low_rank, self.gate_silu = bool(low_rank), gate_act == "silu"
         self.hidden, self.H, self.G, self.dim, self.vdim = hidden, num_heads, num_qk_heads, dim, vdim
         self.taps, self.eps, self.names = int(conv_taps), float(eps), dict(names)
         self.out_scale, self.float_out, self.rank = float(out_scale), bool(float_out), int(rank)
@@ -54,20 +62,30 @@ class GatedDeltaRule(Mixer):
         for key, rows in (("q", qk), ("k", qk), ("v", vw)):
             specs.append(ParamSpec(n[key], (rows, W), MATRIX))
             specs.append(ParamSpec(n[key] + ".conv", (rows, self.taps), VECTOR))
-        specs += [ParamSpec(n["b"], (self.H, W), MATRIX),
-                  ParamSpec(n["a1"], (any_rank, W), MATRIX), ParamSpec(n["a2"], (self.H * self.dim, any_rank), MATRIX),
-                  ParamSpec(n["g1"], (any_rank, W), MATRIX), ParamSpec(n["g2"], (vw, any_rank), MATRIX),
-                  ParamSpec(n["A_log"], (self.H,), VECTOR), ParamSpec(n["dt_bias"], (self.H * self.dim,), VECTOR),
-                  ParamSpec(n["norm"], (self.vdim,), GAIN), ParamSpec(n["o"], (W, vw), MATRIX)]
+        specs.append(ParamSpec(n["b"], (self.H, W), MATRIX))
+        if self.low_rank:
+            specs += [ParamSpec(n["a1"], (any_rank, W), MATRIX), ParamSpec(n["a2"], (self.H * self.dim, any_rank), MATRIX),
+                      ParamSpec(n["g1"], (any_rank, W), MATRIX), ParamSpec(n["g2"], (vw, any_rank), MATRIX),
+                      ParamSpec(n["dt_bias"], (self.H * self.dim,), VECTOR)]
+        else:
+            specs += [ParamSpec(n["a"], (self.H, W), MATRIX), ParamSpec(n["g"], (vw, W), MATRIX),
+                      ParamSpec(n["dt_bias"], (self.H,), VECTOR)]
+        specs += [ParamSpec(n["A_log"], (self.H,), VECTOR), ParamSpec(n["norm"], (self.vdim,), GAIN),
+                  ParamSpec(n["o"], (W, vw), MATRIX)]
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
-        a1, g1 = tensors.pop(n["a1"]), tensors.pop(n["g1"])
-        self.w_a2, self.w_g2 = tensors.pop(n["a2"]).contiguous(), tensors.pop(n["g2"]).contiguous()
-        self.rank_a, self.rank_g = a1.shape[0], g1.shape[0]
-        if self.w_a2.shape[1] != self.rank_a or self.w_g2.shape[1] != self.rank_g:
-            raise ValueError(f"the low-rank pairs of '{n['a1']}' / '{n['g1']}' do not agree in their inner size")
+        if self.low_rank:
+            a1, g1 = tensors.pop(n["a1"]), tensors.pop(n["g1"])
+            self.w_a2, self.w_g2 = tensors.pop(n["a2"]).contiguous(), tensors.pop(n["g2"]).contiguous()
+            self.rank_a, self.rank_g = a1.shape[0], g1.shape[0]
+            if self.w_a2.shape[1] != self.rank_a or self.w_g2.shape[1] != self.rank_g:
+                raise ValueError(f"the low-rank pairs of '{n['a1']}' / '{n['g1']}' do not agree in their inner size")
+        else:
+            # the projection's columns hold the decay logits and the gate logits themselves
+            a1, g1 = tensors.pop(n["a"]), tensors.pop(n["g"])
+            self.rank_a, self.rank_g = a1.shape[0], g1.shape[0]
         self.w_in = torch.cat([tensors.pop(n["q"]), tensors.pop(n["k"]), tensors.pop(n["v"]), tensors.pop(n["b"]),
                                a1, g1], dim=0).contiguous()
         self.conv_w = torch.cat([tensors.pop(n[k] + ".conv") for k in "qkv"], dim=0).to(torch.float32).contiguous()
@@ -92,11 +110,11 @@ class GatedDeltaRule(Mixer):
         ops.delta_rule(proj, b_off, a_off, g_off, self.conv_w, tails.state, self.w_a2, self.a_log, self.dt_bias,
                        self.w_g2, self.norm_w, self.eps, self.out_scale, mats.state, mats.writable, single, scratch, o,
                        ctx.positions, ctx.seq_of_token, ctx.q_start, ctx.slots, ctx.n_seqs, self.H, self.G, self.dim,
-                       self.vdim)
+                       self.vdim, gate_silu=self.gate_silu)
         if self.taps > 1 and tails.writable and not (single and mats.writable):
             ops.conv_state_update(proj, self.channels, tails.state, ctx.positions, ctx.q_start, ctx.slots, ctx.n_seqs)
         return Delta(ops.linear(o, self.w_o, out_dtype=torch.float32 if self.float_out else None))
 
     def param_bytes(self) -> int:
-        return ((self.w_in.numel() + self.w_o.numel() + self.w_a2.numel() + self.w_g2.numel())
-                * self.w_in.element_size())
+        low = (self.w_a2.numel() + self.w_g2.numel()) if self.low_rank else 0
+        return (self.w_in.numel() + self.w_o.numel() + low) * self.w_in.element_size()

@@ -6,6 +6,7 @@ bias travels with the result so the next norm kernel adds it with the residual.
 """
 from __future__ import annotations
 
+import math
 from typing import Any, Dict, List, Optional
 
 import torch
@@ -136,3 +137,39 @@ class ClampedGatedFFN(FeedForward):
 
     def param_bytes(self) -> int:
         return (self.w_gu.numel() + self.w_down.numel()) * self.w_gu.element_size()
+
+
+@FEED_FORWARDS.register("dense_xielu")
+class XieluFFN(FeedForward):
+    """z = down(act(up h)), no biases, with the two-sided activation
+
+        act(z) = a_p z^2 + z / 2                    for z > 0
+               = a_n (exp(z) - 1 - z) + z / 2       for z <= 0,     a_p = softplus(p),  a_n = shift + softplus(q),
+
+    whose two numbers (p, q) are the tensor ``act_name`` [2]; ``shift`` is the constant added to softplus(q).  The
+    two factors are formed once, in double precision, when the weights are bound."""
+
+    def __init__(self, hidden: int, inner: int, up_name: str, down_name: str, act_name: str, shift: float = 0.5,
+                 float_out: bool = False):
+        self.hidden, self.inner, self.shift, self.float_out = hidden, inner, float(shift), bool(float_out)
+        self.up_name, self.down_name, self.act_name = up_name, down_name, act_name
+        self.w_up = self.w_down = None
+        self.alpha_pos = self.alpha_neg = 0.0
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec(self.up_name, (self.inner, self.hidden), MATRIX),
+                ParamSpec(self.down_name, (self.hidden, self.inner), MATRIX),
+                ParamSpec(self.act_name, (2,), VECTOR)]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_up, self.w_down = tensors[self.up_name], tensors[self.down_name]
+        p, q = (float(v) for v in tensors[self.act_name].to(torch.float64).cpu())
+        softplus = lambda z: max(z, 0.0) + math.log1p(math.exp(-abs(z)))
+        self.alpha_pos, self.alpha_neg = softplus(p), self.shift + softplus(q)
+
+    def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
+        u = ops.xielu(ops.linear(h, self.w_up), self.alpha_pos, self.alpha_neg)
+        return Delta(ops.linear(u, self.w_down, out_dtype=torch.float32 if self.float_out else None))
+
+    def param_bytes(self) -> int:
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_up.element_size()

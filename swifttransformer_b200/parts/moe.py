@@ -6,6 +6,9 @@
     out = sum over the chosen e of s_e * down_e(act(gate_e h) * (up_e h))
           + sigmoid(w_sg . h) * down_s(act(gate_s h) * (up_s h))          the shared expert, for every token
 
+With ``limit`` the experts are clamped gated units instead: g = min(gate_e h, limit), u = clamp(up_e h, -limit, limit),
+down_e(g * sigmoid(alpha * g) * (u + shift)).
+
 On the device the step's (token, choice) items are grouped by expert (``ops.moe_sort``), two grouped products run
 over the groups (gate|up with the activation in the epilogue, then down), and one kernel forms the weighted sums and
 adds the gated shared expert, in float.  Nothing comes back to the host, so steps are recorded like any others.
@@ -29,7 +32,9 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, hidden: int, inner: int, num_experts: int, top: int, activation: str,
                  expert_names: List[Dict[str, str]], router_name: str, shared: Optional[FeedForward] = None,
-                 shared_gate_name: Optional[str] = None, renormalise: bool = False):
+                 shared_gate_name: Optional[str] = None, renormalise: bool = False, limit: Optional[float] = None,
+                 alpha: float = 1.0, shift: float = 0.0):
+        self.limit, self.alpha, self.shift = (float(limit) if limit else None), float(alpha), float(shift)
         if activation not in ops.ACT_CODES:
             raise ValueError(f"activation '{activation}' is not supported ({', '.join(ops.ACT_CODES)})")
         if len(expert_names) != num_experts or not 1 <= top <= num_experts:
@@ -64,7 +69,12 @@ class RoutedExperts(FeedForward):
     def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
         experts, weights, gate = ops.moe_route(h, self.w_router, self.top, ctx.positions, self.w_sg, self.renormalise)
         order = ops.moe_sort(experts, self.n_experts)
-        u = ops.gemm_experts(h, self.w_gu, order, gather=True, gated=True, act=self.activation)
+        if self.limit is not None:
+            # gate | up of every item as the product leaves them, then the clamped unit over the rows
+            u = ops.gated_clamped_act(ops.gemm_experts(h, self.w_gu, order, gather=True), None, self.limit, self.alpha,
+                                      self.shift)
+        else:
+            u = ops.gemm_experts(h, self.w_gu, order, gather=True, gated=True, act=self.activation)
         y = ops.gemm_experts(u, self.w_down, order, gather=False)
         shared = None
         if self.shared is not None:
