@@ -1393,5 +1393,29 @@ def talk_attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: t
 
 def talk_attention_tiles_applies(q: torch.Tensor, nh: int, nkv: int, dim: int, vd: int) -> bool:
     """Whether the tensor-core kernel for query tiles takes these sizes (bfloat16 only)."""
-    return (q.is_cuda and q.dtype == torch.bfloat16 and hasattr(lib(), "st_talk_attention_tiles_applies")
-            and bool(lib().st_talk_attention_tiles_applies(nh, nkv, dim, vd)))
+    return q.is_cuda and q.dtype == torch.bfloat16 and bool(lib().st_talk_attention_tiles_applies(nh, nkv, dim, vd))
+
+
+def talk_attention_tiles(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, tiles: torch.Tensor,
+                         n_tiles: int, tile_rows: int, q_start: torch.Tensor, start_pos: torch.Tensor,
+                         slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, dim: int, vd: int,
+                         page_size: int, scale: float, window: int, keep_first: int, talk: Optional[torch.Tensor],
+                         sinks: Optional[torch.Tensor], gate: Optional[torch.Tensor], gate_off: int, gate_heads: bool,
+                         out_scale: float, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same attention as ``talk_attention_plain`` for tiles of ``tile_rows`` query rows (tiles: int32 [n_tiles, 2]
+    = request of the step, offset of the tile among its new tokens) on the warp-level tensor cores, bfloat16 only."""
+    if not talk_attention_tiles_applies(q, nh, nkv, dim, vd):
+        raise KernelError("talk_attention_tiles: bfloat16, dim and vd multiples of 8 up to 128, heads within a block")
+    assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
+    stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, None,
+                                               gate, gate_off, out_scale)
+    if talk is not None:
+        assert talk.dtype == torch.float32 and talk.shape == (nh, nh) and talk.is_contiguous()
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.numel() == nh and sinks.is_contiguous()
+    _check(lib().st_talk_attention_tiles(_p(q), _p(pool), stride, off, _p(out), _p(tiles), n_tiles, tile_rows,
+                                         _p(q_start), _p(start_pos), _p(slots), _p(block_table), block_table.shape[1],
+                                         nh, nkv, dim, vd, page_size, _f(scale), window, keep_first, _p(talk), _p(sinks),
+                                         gate_ptr, gate_ld, int(gate_heads), _f(out_scale), _p(status), _stream()),
+           "talk_attention_tiles")
+    return out

@@ -103,8 +103,18 @@ def rotate_halves(u, positions, dims, base):
 
 
 def seen_window(T, size):
+    """[T, T]: query i sees key j when 0 <= i - j < size (size None: every earlier key and itself)."""
     i, j = np.arange(T)[:, None], np.arange(T)[None, :]
-    return (i - j >= 0) & (i - j < size)
+    return (i - j >= 0) & ((i - j < size) if size else True)
+
+
+def window_of(mx):
+    return mx["mask"]["size"] if mx.get("mask") else None
+
+
+def rotated(u, positions, mx):
+    rot = mx.get("rot")
+    return rotate_halves(u, positions, rot["dims"], rot["base"]) if rot else u
 
 
 def softmax_with_sink(s, seen, sink):
@@ -140,9 +150,8 @@ def talking_attention(h, w, p, mx):
     q = (h @ w[p + "q"].T).reshape(T, H, d)
     k = (h @ w[p + "k"].T).reshape(T, G, d)
     v = (h @ w[p + "v"].T).reshape(T, G, e)
-    q = rotate_halves(q, pos, mx["rot"]["dims"], mx["rot"]["base"])
-    k = rotate_halves(k, pos, mx["rot"]["dims"], mx["rot"]["base"])
-    P = attention_weights(q, k, seen_window(T, mx["mask"]["size"]), mx["scale"], w[p + "sink"])
+    q, k = rotated(q, pos, mx), rotated(k, pos, mx)
+    P = attention_weights(q, k, seen_window(T, window_of(mx)), mx["scale"], w[p + "sink"])
     P = np.einsum("ab,bij->aij", w[p + "talk"], P)
     o = apply_weights(P, v)
     o = o * sigmoid(h @ w[p + "g"].T)[:, :, None]
@@ -158,9 +167,8 @@ def gated_attention(h, w, p, mx, eps):
     q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, d)
     k = (h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G, d)
     v = (h @ w[p + "v"].T + w[p + "v.b"]).reshape(T, G, e)
-    q = rms_unit(rotate_halves(q, pos, mx["rot"]["dims"], mx["rot"]["base"]), eps)
-    k = rms_unit(rotate_halves(k, pos, mx["rot"]["dims"], mx["rot"]["base"]), eps)
-    P = attention_weights(q, k, seen_window(T, mx["mask"]["size"]), mx["scale"], w[p + "sink"])
+    q, k = rms_unit(rotated(q, pos, mx), eps), rms_unit(rotated(k, pos, mx), eps)
+    P = attention_weights(q, k, seen_window(T, window_of(mx)), mx["scale"], w[p + "sink"])
     o = apply_weights(P, v).reshape(T, H * e)
     return (o * sigmoid(h @ w[p + "g"].T)) @ w[p + "o"].T
 
@@ -254,7 +262,7 @@ def layer_runs(cfg):
 def sublayer_input(xs, w, hc, norm, canon, eps):
     u = np.einsum("s,stw->tw", w[hc + ".in"], xs)
     h = rms_unit(u, eps) * w[norm]
-    return h + causal_conv(h, w[canon])
+    return h + causal_conv(h, w[canon]) if canon in w else h
 
 
 def streams_update(xs, y, w, hc):
@@ -265,7 +273,7 @@ def forward(cfg, w, tokens, return_layers=False):
     """Logits [T, vocab] of a whole sequence (and the summed residual rows after every layer run)."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][np.asarray(tokens)]
-    xs = np.repeat(x[None], cfg["streams"], axis=0)
+    xs = np.repeat(x[None], cfg.get("streams") or 1, axis=0)
     after = []
     for i in layer_runs(cfg):
         layer, p = cfg["layers"][i], f"l{i}."
