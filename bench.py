@@ -15,7 +15,7 @@ batch of requests of random lengths (prompt portions of 512 tokens beside decode
 ``LLMEngine.generate`` and reports tokens per second, steps and preemptions.  ``--only designs`` measures a
 Fanidra, a Pikadra and a Norelix model beside an OPT model of equal width, depth and parameter count (prefill, decode,
 and the device time of every operation of one step of each kind; ``--model-name w2048|w4096`` picks one size,
-``--layers`` the depth, ``--designs`` which of the four).
+``--layers`` the depth, ``--designs`` which of the five).
 """
 import argparse
 import json
@@ -108,6 +108,11 @@ def prefill_flops(cfg, n_layers, n):
 # window, four kept first keys) with a gated delta rule (half the recurrence's heads, on half as many query/key heads),
 # alternating with gated grouped attention over all keys; every second of those reads the keys and values of the one
 # before.  With the same feed-forward size its parameter count is within 1 % of the Fanidra model's.
+# The Nafelix model of a size: four residual streams and input convolutions of four taps around every sub-layer; layers
+# that pair the windowed attention with mixed heads (the Norelix pair's head sizes and window) with the per-head-decay
+# delta rule (the Norelix pair's heads), alternating with gated windowed attention (a window as long as the context);
+# feed-forwards alternate between the dense two-matrix form (inner size one and a half times the gated one's: the
+# same parameter count) and eight clamped experts of half the gated inner size, two per token (the same active count).
 DESIGN_SIZES = {
     "w2048": dict(width=2048, opt_heads=32, opt_ffn=8192, heads=16, kv_heads=4, dim=64, vdim=128, ff=5504,
                   rec_heads=16, rec_dim=128, rec_vdim=128, block=512,
@@ -128,7 +133,7 @@ def compare_designs(args, peaks):
     import numpy as np
     import torch
     from swifttransformer_b200 import ops
-    from swifttransformer_b200.config import FanidraConfig, NorelixConfig, OptConfig, PikadraConfig
+    from swifttransformer_b200.config import FanidraConfig, NafelixConfig, NorelixConfig, OptConfig, PikadraConfig
     from swifttransformer_b200.engine.engine import LLMEngine
     from swifttransformer_b200.engine.step import StepEntry
     from swifttransformer_b200.models import random_model
@@ -174,7 +179,17 @@ def compare_designs(args, peaks):
                      for i in range(n_layers)]
         nor = NorelixConfig.from_dict(dict(architecture="Norelix", vocab=vocab, width=z["width"], norm={"eps": 1e-5},
                                            layers=nx_layers))
-        all_designs = {"fanidra": fan, "pikadra": pik, "norelix": nor, "opt": opt}
+        nf_dense = {"kind": "dense", "ff": z["ff"] * 3 // 2 // 64 * 64}
+        nf_moe = {"kind": "moe", "expert": {"ff": z["ff"] // 2 // 64 * 64, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+        nf_left = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5,
+                       mask={"size": z["block"]}, rot={"dims": z["dim"] // 2, "base": 10000.0})
+        nf_att = dict(nf_left, mask={"size": 4096})
+        nf_layers = [{"type": "parallel", "mlp": nf_dense if i % 4 == 0 else nf_moe, "mixer": {"left": nf_left, "right": nx_right}}
+                     if i % 2 == 0 else {"type": "attention", "mlp": nf_moe if i % 4 == 1 else nf_dense, "mixer": nf_att}
+                     for i in range(n_layers)]
+        naf = NafelixConfig.from_dict(dict(architecture="Nafelix", vocab=vocab, width=z["width"], streams=4,
+                                           norm={"eps": 1e-5}, canon={"taps": 4}, layers=nf_layers))
+        all_designs = {"fanidra": fan, "pikadra": pik, "norelix": nor, "nafelix": naf, "opt": opt}
         return {d: c for d, c in all_designs.items() if not args.designs or d in args.designs.split(",")}
 
     def engine(model, graphs=True):
@@ -277,7 +292,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (0: all)")
     ap.add_argument("--designs", default="", help="with --only designs: which designs to measure, with commas between "
-                    "them (fanidra, pikadra, norelix, opt; default: all)")
+                    "them (fanidra, pikadra, norelix, nafelix, opt; default: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-big", action="store_true", help="skip the OPT-6.7B and OPT-30B points (13 and 60 GB of random weights)")
     ap.add_argument("--launch-floor", action="store_true",

@@ -1419,3 +1419,44 @@ def talk_attention_tiles(q: torch.Tensor, pool: torch.Tensor, layer: int, out: t
                                          gate_ptr, gate_ld, int(gate_heads), _f(out_scale), _p(status), _stream()),
            "talk_attention_tiles")
     return out
+
+
+def talk_attention_single_applies(q: torch.Tensor, nh: int, nkv: int, dim: int, vd: int, n_cap: int) -> bool:
+    """Whether the two-kernel form for single tokens takes these sizes (bfloat16; all heads' weights of a token,
+    heads * n_cap floats, within shared memory)."""
+    return (q.is_cuda and q.dtype == torch.bfloat16
+            and bool(lib().st_talk_attention_single_applies(nh, nkv, dim, vd, int(n_cap))))
+
+
+def talk_attention_single_scratch(n_tokens: int, nh: int, n_cap: int) -> int:
+    return int(n_tokens) * int(nh) * int(n_cap)
+
+
+def talk_attention_single(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
+                          seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int,
+                          dim: int, vd: int, page_size: int, scale: float, window: int, keep_first: int,
+                          talk: Optional[torch.Tensor], sinks: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                          gate_off: int, gate_heads: bool, out_scale: float, scratch: torch.Tensor, n_cap: int,
+                          status: Optional[torch.Tensor] = None, items: Optional[torch.Tensor] = None,
+                          n_items: Optional[int] = None) -> torch.Tensor:
+    """The same attention as ``talk_attention_plain`` token by token in bfloat16: raw scores of every (token, head,
+    seen key) into ``scratch`` (float32, ``talk_attention_single_scratch`` elements), then softmax, mixing and values
+    per (token, key/value head).  ``n_cap``: the most keys a token of the step sees."""
+    if not talk_attention_single_applies(q, nh, nkv, dim, vd, n_cap):
+        raise KernelError("talk_attention_single: bfloat16, dim and vd multiples of 8, vd <= 256, at most eight query "
+                          "heads per key/value head, and all heads' weights of a token within shared memory")
+    assert q.is_contiguous() and out.is_contiguous() and out.shape == (q.shape[0], nh * vd)
+    stride, off, gate_ptr, gate_ld = _gqa_tail(pool, layer, nkv, dim, vd, page_size, scale, window, keep_first, None,
+                                               gate, gate_off, out_scale)
+    n = q.shape[0] if items is None else (n_items if n_items is not None else items.numel())
+    assert scratch.dtype == torch.float32 and scratch.numel() >= talk_attention_single_scratch(n, nh, n_cap)
+    if talk is not None:
+        assert talk.dtype == torch.float32 and talk.shape == (nh, nh) and talk.is_contiguous()
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.numel() == nh and sinks.is_contiguous()
+    _check(lib().st_talk_attention_single(_p(q), _p(pool), stride, off, _p(out), _p(items), _p(positions),
+                                          _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1], n, nh, nkv,
+                                          dim, vd, page_size, _f(scale), window, keep_first, _p(talk), _p(sinks),
+                                          gate_ptr, gate_ld, int(gate_heads), _f(out_scale), _p(scratch), int(n_cap),
+                                          _p(status), _stream()), "talk_attention_single")
+    return out

@@ -158,16 +158,26 @@ class GroupedAttention(Mixer):
             tail = (self.nh, self.nkv, self.dim, self.vdim, ps, self.scale, self.window or 0, self.keep_first, self.talk,
                     self._sink_vector(h.device), gate, gate_off, self.gate_heads, self.out_scale)
             plan = ctx.plan(PagedAttentionPlan.name)
-            fast = ops.talk_attention_tiles_applies(q, self.nh, self.nkv, self.dim, self.vdim)
-            if fast and plan.n_tiles:
-                ops.talk_attention_tiles(q, *args, plan.tiles, plan.n_tiles, self._plan.tile_rows, ctx.q_start,
-                                         ctx.start_pos, ctx.slots, cache.block_table, *tail, status=ctx.status)
-                if plan.n_items:
-                    ops.talk_attention_plain(q, *args, ctx.positions, ctx.seq_of_token, ctx.slots, cache.block_table,
-                                             *tail, status=ctx.status, items=plan.items, n_items=plan.n_items)
+            rows = (ctx.positions, ctx.seq_of_token, ctx.slots, cache.block_table)
+            tiles_ok = ops.talk_attention_tiles_applies(q, self.nh, self.nkv, self.dim, self.vdim)
+            if h.dtype != torch.bfloat16 or (plan.n_tiles and not tiles_ok):
+                ops.talk_attention_plain(q, *args, *rows, *tail, status=ctx.status)
             else:
-                ops.talk_attention_plain(q, *args, ctx.positions, ctx.seq_of_token, ctx.slots, cache.block_table, *tail,
-                                         status=ctx.status)
+                if plan.n_tiles:
+                    ops.talk_attention_tiles(q, *args, plan.tiles, plan.n_tiles, self._plan.tile_rows, ctx.q_start,
+                                             ctx.start_pos, ctx.slots, cache.block_table, *tail, status=ctx.status)
+                if plan.n_items:
+                    # the most keys a token of the step sees
+                    cap = max(int(plan.max_item_kv), 1)
+                    if self.window:
+                        cap = min(cap, self.window + self.keep_first)
+                    if ops.talk_attention_single_applies(q, self.nh, self.nkv, self.dim, self.vdim, cap):
+                        scratch = ctx.scratch_f32(ops.talk_attention_single_scratch(plan.n_items, self.nh, cap))
+                        ops.talk_attention_single(q, *args, *rows, *tail, scratch, cap, status=ctx.status,
+                                                  items=plan.items, n_items=plan.n_items)
+                    else:
+                        ops.talk_attention_plain(q, *args, *rows, *tail, status=ctx.status, items=plan.items,
+                                                 n_items=plan.n_items)
             return Delta(ops.linear(o, self.w_o, out_dtype=torch.float32 if self.float_out else None), self.b_o)
         consts = (self.nh, self.nkv, self.dim, self.vdim, ps, self.scale, self.window or 0, self.keep_first, sink,
                   gate, gate_off, self.out_scale)
