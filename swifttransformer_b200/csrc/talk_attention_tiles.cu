@@ -21,8 +21,7 @@
 
 #define TT_ROWS 16
 #define TT_KEYS 32
-#define TT_THREADS 256
-#define TT_WARPS 8
+#define TT_MAX_THREADS 512
 
 template <int DIMT, int VDT>
 struct TalkTileSmem {
@@ -35,7 +34,7 @@ struct TalkTileSmem {
 };
 
 // keys key0 .. key0 + 31 of every key/value head into a stage: keys [nkv][32][K_LD], then values [nkv][32][V_LD]
-template <int DIMT, int VDT>
+template <int DIMT, int VDT, int THREADS>
 __device__ __forceinline__ void talk_load_kv_tile(bf16* stage, const bf16* __restrict__ pool, const DiffCache& cache,
                                                   const int* __restrict__ bt, int key0, int lo, int hi, int keep_first,
                                                   int* __restrict__ status) {
@@ -44,8 +43,9 @@ __device__ __forceinline__ void talk_load_kv_tile(bf16* stage, const bf16* __res
     const int nkv = cache.nkv, dim = cache.kd, vd = cache.vd, ps = cache.page_size;
     bf16* sk = stage;
     bf16* sv = stage + (size_t)nkv * TT_KEYS * L::K_LD;
-    // eight threads per key: one look-up of its page, then the pieces of its rows in every key/value head
-    const int row = threadIdx.x >> 3, sub = threadIdx.x & 7;
+    // THREADS / 32 threads per key: one look-up of its page, then the pieces of its rows in every key/value head
+    constexpr int PER = THREADS / TT_KEYS;
+    const int row = threadIdx.x / PER, sub = threadIdx.x % PER;
     const int key = key0 + row;
     int page = -1;
     if (key <= hi && (key >= lo || key < keep_first)) {
@@ -53,7 +53,7 @@ __device__ __forceinline__ void talk_load_kv_tile(bf16* stage, const bf16* __res
         if (page < 0 && status) *status = 1;
     }
     const int pip = key % ps;
-    for (int c = sub; c < nkv * (KC + VC); c += 8) {
+    for (int c = sub; c < nkv * (KC + VC); c += PER) {
         const int kvh = c / (KC + VC), p = c % (KC + VC);
         if (p < KC) {
             const int e = p * 8;
@@ -69,8 +69,8 @@ __device__ __forceinline__ void talk_load_kv_tile(bf16* stage, const bf16* __res
     }
 }
 
-template <int DIMT, int VDT, int HPW>
-__global__ void __launch_bounds__(TT_THREADS)
+template <int DIMT, int VDT, int HPW, int TT_WARPS>
+__global__ void __launch_bounds__(TT_WARPS * 32)
 talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, DiffCache cache,
                             bf16* __restrict__ out, const int* __restrict__ tiles, int parts,
                             const int* __restrict__ q_start, const int* __restrict__ start_pos,
@@ -78,6 +78,7 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             GqaMask mask, const float* __restrict__ talk, int has_sink, GqaEpilogue epi, int gate_heads,
                             int* __restrict__ status) {
     using L = TalkTileSmem<DIMT, VDT>;
+    constexpr int TT_THREADS = TT_WARPS * 32;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int nkv = cache.nkv, vd = cache.vd, dim = cache.kd;
     bf16* stages = reinterpret_cast<bf16*>(smem_raw);
@@ -134,44 +135,60 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 #define TT_TILE(i) ((i) < n_a ? (i) : k_b + (i) - n_a)
 
     // S of head (warp + 8 i) for the stage's 32 keys, masked, in units of log2(e)
-    auto scores = [&](const bf16* stage, int i, int key0, float (&s)[TT_KEYS / 8][4]) {
+    auto scores = [&](const bf16* stage, int i, int key0, bool inside, float (&s)[TT_KEYS / 8][4]) {
         const int h = warp + TT_WARPS * i;
         const bf16* sk = stage + (size_t)(h / rep) * TT_KEYS * L::K_LD;
 #pragma unroll
         for (int nt = 0; nt < TT_KEYS / 8; ++nt) {
 #pragma unroll
             for (int x = 0; x < 4; ++x) s[nt][x] = 0.f;
+            // the column operand of two steps of k at once: four 8 x 8 pieces of the tile's rows nt * 8 .. + 7
 #pragma unroll
-            for (int ks = 0; ks < DIMT / 16; ++ks) {
-                const bf16* kp = sk + (nt * 8 + g) * L::K_LD + ks * 16 + 2 * tq;
-                mma_bf16(s[nt], qa[i][ks], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+            for (int ks = 0; ks < DIMT / 16; ks += 2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, sk + (nt * 8 + (lane & 7)) * L::K_LD + ks * 16 + (lane >> 3) * 8);
+                mma_bf16(s[nt], qa[i][ks], b0, b1);
+                mma_bf16(s[nt], qa[i][ks + 1], b2, b3);
             }
+            if (inside) {
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const int r = x >> 1, key = key0 + nt * 8 + 2 * tq + (x & 1);
-                s[nt][x] = (live[r] && gqa_seen(key, pos[r], mask)) ? s[nt][x] * scale_l2 : -INFINITY;
+                for (int x = 0; x < 4; ++x) s[nt][x] *= scale_l2;
+            } else {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const int r = x >> 1, key = key0 + nt * 8 + 2 * tq + (x & 1);
+                    s[nt][x] = (live[r] && gqa_seen(key, pos[r], mask)) ? s[nt][x] * scale_l2 : -INFINITY;
+                }
             }
         }
     };
+    // a tile that every one of the block's sixteen rows sees whole takes no mask
+    const int lo_last = gqa_lo(p_first + TT_ROWS - 1, mask);
+    auto whole = [&](int key0) {
+        return rows_here == TT_ROWS && key0 + TT_KEYS - 1 <= p_first &&
+               (mask.window <= 0 || key0 >= lo_last || key0 + TT_KEYS <= keep);
+    };
 
-    // ---- first walk: maxima and sums
-    talk_load_kv_tile<DIMT, VDT>(stages, pool, cache, bt, TT_TILE(0) * TT_KEYS, lo, hi, keep, status);
+    // ---- first walk: maxima and sums.  One barrier per tile: behind it the tile has landed for every thread and
+    // every warp is done with the tile before, whose stage the copies of the next tile may then fill.
+    talk_load_kv_tile<DIMT, VDT, TT_THREADS>(stages, pool, cache, bt, TT_TILE(0) * TT_KEYS, lo, hi, keep, status);
     cp_async_commit();
     for (int t = 0; t < n_t; ++t) {
         const bf16* stage = stages + (t & 1) * stage_elems;
+        cp_async_wait<0>();
+        __syncthreads();
         // behind the last tile of this walk the first tile of the second walk is already asked for
         const int nxt = t + 1 < n_t ? t + 1 : 0;
-        talk_load_kv_tile<DIMT, VDT>(stages + ((t + 1) & 1) * stage_elems, pool, cache, bt, TT_TILE(nxt) * TT_KEYS, lo, hi,
+        talk_load_kv_tile<DIMT, VDT, TT_THREADS>(stages + ((t + 1) & 1) * stage_elems, pool, cache, bt, TT_TILE(nxt) * TT_KEYS, lo, hi,
                                      keep, status);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
         const int key0 = TT_TILE(t) * TT_KEYS;
+        const bool inside = whole(key0);
 #pragma unroll
         for (int i = 0; i < HPW; ++i) {
             if (warp + TT_WARPS * i >= nh) continue;
             float s[TT_KEYS / 8][4];
-            scores(stage, i, key0, s);
+            scores(stage, i, key0, inside, s);
             float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int nt = 0; nt < TT_KEYS / 8; ++nt)
@@ -197,7 +214,6 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                 m[i][r] = m_new[r];
             }
         }
-        __syncthreads();
     }
     // the extra term; from here on l holds 1 / denominator
 #pragma unroll
@@ -228,19 +244,20 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     for (int t = 0; t < n_t; ++t) {
         const int u = n_t + t;
         const bf16* stage = stages + (u & 1) * stage_elems;
+        cp_async_wait<0>();
+        __syncthreads();            // the tile has landed; every warp is done with the tile before and its weights
         if (t + 1 < n_t)
-            talk_load_kv_tile<DIMT, VDT>(stages + ((u + 1) & 1) * stage_elems, pool, cache, bt, TT_TILE(t + 1) * TT_KEYS, lo,
+            talk_load_kv_tile<DIMT, VDT, TT_THREADS>(stages + ((u + 1) & 1) * stage_elems, pool, cache, bt, TT_TILE(t + 1) * TT_KEYS, lo,
                                          hi, keep, status);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
         const int key0 = TT_TILE(t) * TT_KEYS;
+        const bool inside = whole(key0);
 #pragma unroll
         for (int i = 0; i < HPW; ++i) {
             const int h = warp + TT_WARPS * i;
             if (h >= nh) continue;
             float s[TT_KEYS / 8][4];
-            scores(stage, i, key0, s);
+            scores(stage, i, key0, inside, s);
 #pragma unroll
             for (int nt = 0; nt < TT_KEYS / 8; ++nt) {
                 float4 p;
@@ -287,7 +304,6 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                     mma_bf16(o[i][2 * nt2 + 1], pa[ks], b2, b3);
                 }
         }
-        __syncthreads();            // the stage and the weights may be written again
     }
 #undef TT_TILE
     cp_async_wait<0>();
@@ -321,34 +337,45 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 
 static int talk_round(int n) { return n <= 32 ? 32 : (n <= 64 ? 64 : 128); }
 
+// Warps per block and heads per warp.  Sixteen warps (a head per warp up to sixteen heads) when the registers of 512
+// threads hold it: a warp's sums are then vd / 2 floats per lane, and four warps per scheduler hide one another's waits
+// (measured); else eight warps with up to four heads each.
+static void talk_split(int nh, int dimt, int vdt, int* warps, int* hpw) {
+    const int h16 = (nh + 15) / 16;
+    if (h16 == 1 && vdt <= 128 && dimt <= 64) { *warps = 16; *hpw = 1; return; }
+    *warps = 8;
+    *hpw = (nh + 7) / 8;
+}
+
 // bfloat16; dim and vd multiples of 8 up to 128; at most 32 heads, and heads per warp x vd within the registers;
 // the stages and the weights within shared memory
 ST_EXPORT int st_talk_attention_tiles_applies(int nh, int nkv, int dim, int vd) {
     if (nh <= 0 || nkv <= 0 || nh % nkv || dim <= 0 || vd <= 0 || dim % 8 || vd % 8 || dim > 128 || vd > 128) return 0;
-    const int hpw = (nh + TT_WARPS - 1) / TT_WARPS;
     const int dimt = talk_round(dim), vdt = talk_round(vd);
+    int warps, hpw;
+    talk_split(nh, dimt, vdt, &warps, &hpw);
     if (hpw > 4 || hpw * vdt > 256 || hpw * dimt > 256) return 0;
     const size_t smem = 2 * (size_t)nkv * TT_KEYS * (dimt + 8 + vdt + 8) * sizeof(bf16) +
                         ((size_t)nh * TT_KEYS * TT_ROWS + (size_t)nh * nh) * sizeof(float);
     return smem <= 200 * 1024;
 }
 
-template <int DIMT, int VDT, int HPW>
+template <int DIMT, int VDT, int HPW, int WARPS>
 static int launch_talk_tiles(const void* q, const void* pool, const DiffCache& c, void* out, const int* tiles, int n_tiles,
                              int tile_rows, const int* q_start, const int* start_pos, const int* slots,
                              const int* block_table, int nh, float scale, const GqaMask& mask, const float* talk,
                              int has_sink, const GqaEpilogue& epi, int gate_heads, int* status, cudaStream_t s) {
-    if constexpr (HPW * VDT > 256 || HPW * DIMT > 256) {
+    if constexpr (HPW * VDT > 256 || HPW * DIMT > 256 || (WARPS == 16 && (HPW != 1 || DIMT > 64))) {
         return ST_ERR_BAD_SIZE;
     } else {
         const size_t smem = TalkTileSmem<DIMT, VDT>::bytes(nh, c.nkv);
-        auto kern = talk_attention_tiles_kernel<DIMT, VDT, HPW>;
+        auto kern = talk_attention_tiles_kernel<DIMT, VDT, HPW, WARPS>;
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
         const int parts = (tile_rows + TT_ROWS - 1) / TT_ROWS;
-        kern<<<dim3(n_tiles * parts), TT_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, c, (bf16*)out, tiles, parts,
+        kern<<<dim3(n_tiles * parts), WARPS * 32, smem, s>>>((const bf16*)q, (const bf16*)pool, c, (bf16*)out, tiles, parts,
                                                             q_start, start_pos, slots, block_table, nh, scale, mask, talk,
                                                             has_sink, epi, gate_heads, status);
         return st_launch_status();
@@ -370,15 +397,17 @@ ST_EXPORT int st_talk_attention_tiles(const void* q, const void* pool, long long
     const GqaMask mask = {window, keep_first};
     const GqaEpilogue epi = {gate, gate_ld, out_scale, sinks};
     cudaStream_t s = (cudaStream_t)stream;
-    const int hpw = (nh + TT_WARPS - 1) / TT_WARPS;
     const int dimt = talk_round(dim), vdt = talk_round(vd);
+    int warps, hpw;
+    talk_split(nh, dimt, vdt, &warps, &hpw);
 #define TT_ARGS q, pool, c, out, tiles, n_tiles, tile_rows, q_start, start_pos, slots, block_table, nh, scale, mask, talk, \
                 sinks != nullptr, epi, gate_heads, status, s
-#define TT_BY_HEADS(D, V)                                          \
-    do {                                                           \
-        if (hpw == 1) return launch_talk_tiles<D, V, 1>(TT_ARGS);  \
-        if (hpw == 2) return launch_talk_tiles<D, V, 2>(TT_ARGS);  \
-        return launch_talk_tiles<D, V, 4>(TT_ARGS);                \
+#define TT_BY_HEADS(D, V)                                                          \
+    do {                                                                           \
+        if (warps == 16) return launch_talk_tiles<D, V, 1, 16>(TT_ARGS);           \
+        if (hpw == 1) return launch_talk_tiles<D, V, 1, 8>(TT_ARGS);               \
+        if (hpw == 2) return launch_talk_tiles<D, V, 2, 8>(TT_ARGS);               \
+        return launch_talk_tiles<D, V, 4, 8>(TT_ARGS);                             \
     } while (0)
 #define TT_BY_V(D)                            \
     do {                                      \
