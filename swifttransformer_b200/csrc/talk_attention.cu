@@ -15,7 +15,7 @@
 #include "gqa_attention.cuh"
 
 #define TK 128            // keys per tile == threads per block
-#define T_ACC 16          // outputs (head, value dimension) per thread: heads * vd <= T_ACC * TK
+#define T_ACC 64          // outputs (head, value dimension) per thread: heads * vd <= T_ACC * TK
 
 // gate_heads != 0: one gate logit per head at gate[token * gate_ld + head]; else one per (head, e).
 template <typename T>

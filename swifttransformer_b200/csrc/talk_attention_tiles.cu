@@ -33,14 +33,15 @@ struct TalkTileSmem {
     }
 };
 
-// keys key0 .. key0 + 31 of every key/value head into a stage: keys [nkv][32][K_LD], then values [nkv][32][V_LD]
+// keys key0 .. key0 + 31 of every key/value head into a stage: keys [nkv][32][K_LD], then the block's part of the
+// values (columns e0 .. e0 + vd_block - 1 of every row) [nkv][32][V_LD]
 template <int DIMT, int VDT, int THREADS>
 __device__ __forceinline__ void talk_load_kv_tile(bf16* stage, const bf16* __restrict__ pool, const DiffCache& cache,
                                                   const int* __restrict__ bt, int key0, int lo, int hi, int keep_first,
-                                                  int* __restrict__ status) {
+                                                  int e0, int vd_block, int* __restrict__ status) {
     using L = TalkTileSmem<DIMT, VDT>;
     constexpr int KC = DIMT / 8, VC = VDT / 8;
-    const int nkv = cache.nkv, dim = cache.kd, vd = cache.vd, ps = cache.page_size;
+    const int nkv = cache.nkv, dim = cache.kd, ps = cache.page_size;
     bf16* sk = stage;
     bf16* sv = stage + (size_t)nkv * TT_KEYS * L::K_LD;
     // THREADS / 32 threads per key: one look-up of its page, then the pieces of its rows in every key/value head
@@ -63,7 +64,7 @@ __device__ __forceinline__ void talk_load_kv_tile(bf16* stage, const bf16* __res
         } else {
             const int e = (p - KC) * 8;
             bf16* dst = sv + ((size_t)kvh * TT_KEYS + row) * L::V_LD + e;
-            if (page >= 0 && e < vd) cp_async16(dst, cache_values(pool, cache, page, kvh, pip) + e, true);
+            if (page >= 0 && e < vd_block) cp_async16(dst, cache_values(pool, cache, page, kvh, pip) + e0 + e, true);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
     }
@@ -92,6 +93,9 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int first = q_start[req], n_new = q_start[req + 1] - first;
     if (off >= n_new) return;
     const int rep = nh / nkv;
+    // the value columns this block serves: a model whose heads x vd do not fit one block's registers is served by
+    // gridDim.y blocks per sixteen rows, each with all the scores and weights and a part of every value row
+    const int vd_block = vd / gridDim.y, e0 = blockIdx.y * vd_block;
     const int start = start_pos[req];
     const int* bt = block_table + (size_t)slots[req] * cache.max_pages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
@@ -171,7 +175,7 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 
     // ---- first walk: maxima and sums.  One barrier per tile: behind it the tile has landed for every thread and
     // every warp is done with the tile before, whose stage the copies of the next tile may then fill.
-    talk_load_kv_tile<DIMT, VDT, TT_THREADS>(stages, pool, cache, bt, TT_TILE(0) * TT_KEYS, lo, hi, keep, status);
+    talk_load_kv_tile<DIMT, VDT, TT_THREADS>(stages, pool, cache, bt, TT_TILE(0) * TT_KEYS, lo, hi, keep, e0, vd_block, status);
     cp_async_commit();
     for (int t = 0; t < n_t; ++t) {
         const bf16* stage = stages + (t & 1) * stage_elems;
@@ -180,7 +184,7 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         // behind the last tile of this walk the first tile of the second walk is already asked for
         const int nxt = t + 1 < n_t ? t + 1 : 0;
         talk_load_kv_tile<DIMT, VDT, TT_THREADS>(stages + ((t + 1) & 1) * stage_elems, pool, cache, bt, TT_TILE(nxt) * TT_KEYS, lo, hi,
-                                     keep, status);
+                                     keep, e0, vd_block, status);
         cp_async_commit();
         const int key0 = TT_TILE(t) * TT_KEYS;
         const bool inside = whole(key0);
@@ -248,7 +252,7 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         __syncthreads();            // the tile has landed; every warp is done with the tile before and its weights
         if (t + 1 < n_t)
             talk_load_kv_tile<DIMT, VDT, TT_THREADS>(stages + ((u + 1) & 1) * stage_elems, pool, cache, bt, TT_TILE(t + 1) * TT_KEYS, lo,
-                                         hi, keep, status);
+                                         hi, keep, e0, vd_block, status);
         cp_async_commit();
         const int key0 = TT_TILE(t) * TT_KEYS;
         const bool inside = whole(key0);
@@ -316,14 +320,14 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         for (int r = 0; r < 2; ++r) {
             if (!live[r]) continue;
             const size_t t = (size_t)(first + off + g + 8 * r);
-            bf16* orow = out + (t * nh + h) * vd;
+            bf16* orow = out + (t * nh + h) * vd + e0;
             float gh = epi.out_scale;
             if (gate && gate_heads) gh *= sigmoidf_(to_f32(gate[t * epi.gate_ld + h]));
-            const bf16* grow = (gate && !gate_heads) ? gate + t * epi.gate_ld + (size_t)h * vd : nullptr;
+            const bf16* grow = (gate && !gate_heads) ? gate + t * epi.gate_ld + (size_t)h * vd + e0 : nullptr;
 #pragma unroll
             for (int nt = 0; nt < VDT / 8; ++nt) {
                 const int e = nt * 8 + 2 * tq;
-                if (e >= vd) continue;
+                if (e >= vd_block) continue;
                 float a = o[i][nt][2 * r] * gh, b = o[i][nt][2 * r + 1] * gh;
                 if (grow) {
                     a *= sigmoidf_(to_f32(grow[e]));
@@ -337,45 +341,53 @@ talk_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 
 static int talk_round(int n) { return n <= 32 ? 32 : (n <= 64 ? 64 : 128); }
 
-// Warps per block and heads per warp.  Sixteen warps (a head per warp up to sixteen heads) when the registers of 512
-// threads hold it: a warp's sums are then vd / 2 floats per lane, and four warps per scheduler hide one another's waits
-// (measured); else eight warps with up to four heads each.
-static void talk_split(int nh, int dimt, int vdt, int* warps, int* hpw) {
-    const int h16 = (nh + 15) / 16;
-    if (h16 == 1 && vdt <= 128 && dimt <= 64) { *warps = 16; *hpw = 1; return; }
-    *warps = 8;
-    *hpw = (nh + 7) / 8;
+// How a model's heads are laid over a block: blocks per sixteen rows (each with a part of every value row), warps per
+// block, heads per warp.  Sixteen warps when the registers of 512 threads hold a warp's heads (its sums are heads x
+// vd / 2 floats per lane): four warps per scheduler hide one another's waits (measured: a fifth faster than eight
+// warps with two heads each); else eight warps with up to four heads each; else the value rows are cut in two or four.
+#define TT_SMEM_LIMIT (224 * 1024)
+static bool talk_split(int nh, int nkv, int dim, int vd, int* v_parts, int* warps, int* hpw) {
+    const int dimt = talk_round(dim);
+    for (int parts = 1; parts <= 4; parts *= 2) {
+        if (vd % (8 * parts)) break;
+        const int vdt = talk_round(vd / parts);
+        const size_t smem = 2 * (size_t)nkv * TT_KEYS * (dimt + 8 + vdt + 8) * sizeof(bf16) +
+                            ((size_t)nh * TT_KEYS * TT_ROWS + (size_t)nh * nh) * sizeof(float);
+        if (smem > TT_SMEM_LIMIT) continue;
+        const int h16 = (nh + 15) / 16, h8 = (nh + 7) / 8;
+        if (h16 <= 2 && h16 * vdt <= 128 && h16 * dimt <= 128) { *v_parts = parts; *warps = 16; *hpw = h16; return true; }
+        const int h8t = h8 <= 2 ? h8 : 4;
+        if (h8 <= 4 && h8t * vdt <= 256 && h8t * dimt <= 256) { *v_parts = parts; *warps = 8; *hpw = h8t; return true; }
+    }
+    return false;
 }
 
-// bfloat16; dim and vd multiples of 8 up to 128; at most 32 heads, and heads per warp x vd within the registers;
-// the stages and the weights within shared memory
+// bfloat16; dim and vd multiples of 8 up to 128; the heads within the registers of one block (with the value rows cut in
+// up to four parts), the stages and the weights within shared memory
 ST_EXPORT int st_talk_attention_tiles_applies(int nh, int nkv, int dim, int vd) {
     if (nh <= 0 || nkv <= 0 || nh % nkv || dim <= 0 || vd <= 0 || dim % 8 || vd % 8 || dim > 128 || vd > 128) return 0;
-    const int dimt = talk_round(dim), vdt = talk_round(vd);
-    int warps, hpw;
-    talk_split(nh, dimt, vdt, &warps, &hpw);
-    if (hpw > 4 || hpw * vdt > 256 || hpw * dimt > 256) return 0;
-    const size_t smem = 2 * (size_t)nkv * TT_KEYS * (dimt + 8 + vdt + 8) * sizeof(bf16) +
-                        ((size_t)nh * TT_KEYS * TT_ROWS + (size_t)nh * nh) * sizeof(float);
-    return smem <= 200 * 1024;
+    int v_parts, warps, hpw;
+    return talk_split(nh, nkv, dim, vd, &v_parts, &warps, &hpw) ? 1 : 0;
 }
 
 template <int DIMT, int VDT, int HPW, int WARPS>
 static int launch_talk_tiles(const void* q, const void* pool, const DiffCache& c, void* out, const int* tiles, int n_tiles,
                              int tile_rows, const int* q_start, const int* start_pos, const int* slots,
                              const int* block_table, int nh, float scale, const GqaMask& mask, const float* talk,
-                             int has_sink, const GqaEpilogue& epi, int gate_heads, int* status, cudaStream_t s) {
-    if constexpr (HPW * VDT > 256 || HPW * DIMT > 256 || (WARPS == 16 && (HPW != 1 || DIMT > 64))) {
+                             int has_sink, const GqaEpilogue& epi, int gate_heads, int v_parts, int* status,
+                             cudaStream_t s) {
+    if constexpr (HPW * VDT > 256 || HPW * DIMT > 256 || (WARPS == 16 && (HPW > 2 || HPW * VDT > 128 || HPW * DIMT > 128))) {
         return ST_ERR_BAD_SIZE;
     } else {
         const size_t smem = TalkTileSmem<DIMT, VDT>::bytes(nh, c.nkv);
+        if (smem > TT_SMEM_LIMIT) return ST_ERR_TOO_LARGE;
         auto kern = talk_attention_tiles_kernel<DIMT, VDT, HPW, WARPS>;
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
         const int parts = (tile_rows + TT_ROWS - 1) / TT_ROWS;
-        kern<<<dim3(n_tiles * parts), WARPS * 32, smem, s>>>((const bf16*)q, (const bf16*)pool, c, (bf16*)out, tiles, parts,
+        kern<<<dim3(n_tiles * parts, v_parts), WARPS * 32, smem, s>>>((const bf16*)q, (const bf16*)pool, c, (bf16*)out, tiles, parts,
                                                             q_start, start_pos, slots, block_table, nh, scale, mask, talk,
                                                             has_sink, epi, gate_heads, status);
         return st_launch_status();
@@ -397,14 +409,15 @@ ST_EXPORT int st_talk_attention_tiles(const void* q, const void* pool, long long
     const GqaMask mask = {window, keep_first};
     const GqaEpilogue epi = {gate, gate_ld, out_scale, sinks};
     cudaStream_t s = (cudaStream_t)stream;
-    const int dimt = talk_round(dim), vdt = talk_round(vd);
-    int warps, hpw;
-    talk_split(nh, dimt, vdt, &warps, &hpw);
+    int v_parts, warps, hpw;
+    if (!talk_split(nh, nkv, dim, vd, &v_parts, &warps, &hpw)) return ST_ERR_BAD_SIZE;
+    const int dimt = talk_round(dim), vdt = talk_round(vd / v_parts);
 #define TT_ARGS q, pool, c, out, tiles, n_tiles, tile_rows, q_start, start_pos, slots, block_table, nh, scale, mask, talk, \
-                sinks != nullptr, epi, gate_heads, status, s
+                sinks != nullptr, epi, gate_heads, v_parts, status, s
 #define TT_BY_HEADS(D, V)                                                          \
     do {                                                                           \
-        if (warps == 16) return launch_talk_tiles<D, V, 1, 16>(TT_ARGS);           \
+        if (warps == 16 && hpw == 1) return launch_talk_tiles<D, V, 1, 16>(TT_ARGS); \
+        if (warps == 16) return launch_talk_tiles<D, V, 2, 16>(TT_ARGS);           \
         if (hpw == 1) return launch_talk_tiles<D, V, 1, 8>(TT_ARGS);               \
         if (hpw == 2) return launch_talk_tiles<D, V, 2, 8>(TT_ARGS);               \
         return launch_talk_tiles<D, V, 4, 8>(TT_ARGS);                             \

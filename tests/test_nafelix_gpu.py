@@ -249,6 +249,8 @@ TALK_SHAPES = [  # H, G, d, vd, ps, window, talk, sinks, gate
     (16, 4, 40, 48, 32, 130, True, True, "head"),     # pages of 32; a window longer than a tile of queries
     (2, 1, 128, 128, 16, 100, False, True, "head"),   # no mixing matrix: the identity
     (1, 1, 8, 8, 8, 1, True, True, "head"),           # one head, a window of one key
+    (32, 8, 64, 128, 16, 100, True, True, "head"),    # more heads than one block's registers hold: value rows cut in two
+    (24, 4, 32, 64, 8, 40, True, True, "element"),    # two heads per warp of sixteen
 ]
 
 
