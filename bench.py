@@ -13,7 +13,7 @@ single-GPU and exits with 2.
 ``--only decode|prefill`` run one small measurement (for profiling); ``--only mixed`` runs a continuous
 batch of requests of random lengths (prompt portions of 512 tokens beside decoded tokens) through
 ``LLMEngine.generate`` and reports tokens per second, steps and preemptions.  ``--only designs`` measures a
-Fanidra, a Pikadra and a Norelix model beside an OPT model of equal width, depth and parameter count (prefill, decode,
+Fanidra, a Pikadra, a Norelix and a Nafelix model beside an OPT model of equal width, depth and parameter count (prefill, decode,
 and the device time of every operation of one step of each kind; ``--model-name w2048|w4096`` picks one size,
 ``--layers`` the depth, ``--designs`` which of the five).
 """
@@ -126,8 +126,8 @@ DESIGN_SIZES = {
 
 
 def compare_designs(args, peaks):
-    """Prefill (2048 tokens) and decode (batch 8 behind 512-token prompts) of a Fanidra model, a Pikadra model and
-    an OPT model of equal size, random weights, device-timed; and the device time of every operation of one prefill step and one
+    """Prefill (2048 tokens) and decode (batch 8 behind 512-token prompts) of a Fanidra, a Pikadra, a Norelix, a Nafelix
+    and an OPT model of equal size, random weights, device-timed; and the device time of every operation of one prefill step and one
     decode step launched kernel by kernel.  One JSON line per (size, design)."""
     import gc
     import numpy as np

@@ -566,7 +566,7 @@ CONFIGS = {
     "fast": dict(cfg=dict(architecture="Nafelix", vocab=200, width=64, streams=2, norm={"eps": 3e-6}, canon={"taps": 5},
                           layers=[
         pair(left(8, 2, 32, 16, 0.18, 40, 16, 1e4), right(4, 2, 16, 16, 4), moe(4, 2, 32, 2.5)),
-        attn(4, 1, 16, 24, 0.25, 130, 16, 5e5, dense(48)),
+        attn(4, 1, 16, 24, 0.25, 130, 16, 3e5, dense(48)),
         pair(left(4, 4, 16, 32, 0.3, 150, 8, 50.0), right(2, 2, 32, 8, 2), dense(64)),
         attn(8, 8, 8, 8, 0.35, 17, 8, 9.0, moe(8, 2, 16, 1.5))]), seed=32, std=0.12, page_size=16),
     # one stream, no input convolutions, a loop that runs once, one head, a window of one key, an attention without
