@@ -6,6 +6,9 @@
 //   u        = sum_s a[s] * lanes[s]                          h = u / sqrt(mean(u^2) + eps) * w      (hc_read_norm)
 //   lanes[t] <- sum_s M[s][t] * lanes[s] + b[t] * y           all t at once from the old lanes        (hc_write)
 //
+// hc_write_read_norm does the update of one sub-layer and the read of the next in one pass over the copies (a block per
+// token: the new values are written back and their mixture is normed while they are still in registers).
+//
 // hc_spread makes the n copies of the embedding's rows, hc_sum adds them up at the end.  a, b [n] and M [n][n]
 // (indexed [from][to]) are float vectors on the device.
 //
@@ -121,6 +124,100 @@ hc_write_kernel(float* __restrict__ lanes, long long lane_stride, int n_streams,
             if (s < n_streams) v = fmaf(m[s * n_streams + t], old[s], v);
         lanes[(long long)t * lane_stride + i] = fmaf(b[t], yv, v);
     }
+}
+
+// The update of the sub-layer that just ran and the read of the next one, one block per token:
+//   lanes[t] <- sum_s M[s][t] lanes[s] + b[t] y;   u = sum_t a[t] lanes[t];   out = u / rms(u) * gain
+// V = 4: four neighbouring channels per thread (width % 4 == 0), V = 1: any width.
+template <typename TY, int V>
+__global__ void __launch_bounds__(HC_THREADS)
+hc_write_read_norm_kernel(float* __restrict__ lanes, long long lane_stride, int n_streams,
+                          const float* __restrict__ mix, const float* __restrict__ outc, const TY* __restrict__ y,
+                          const float* __restrict__ coef, const float* __restrict__ gain, float eps, int width,
+                          float* __restrict__ out, const int* __restrict__ positions) {
+    __shared__ float m[HC_MAX_STREAMS * HC_MAX_STREAMS], b[HC_MAX_STREAMS], a[HC_MAX_STREAMS];
+    __shared__ float scratch[32];
+    if (threadIdx.x < n_streams * n_streams) m[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < n_streams) { b[threadIdx.x] = outc[threadIdx.x]; a[threadIdx.x] = coef[threadIdx.x]; }
+    __syncthreads();
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int t = blockIdx.x;
+    if (positions && positions[t] < 0) return;
+    float* row = lanes + (size_t)t * width;
+    const TY* yrow = y + (size_t)t * width;
+    float* dst = out + (size_t)t * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x * V; c < width; c += HC_THREADS * V) {
+        float old[HC_MAX_STREAMS][V], yv[V], u[V];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s) {
+            if (s >= n_streams) break;
+            if (V == 4) {
+                const float4 v = load4_cg(row + (size_t)s * lane_stride + c);
+                old[s][0] = v.x; old[s][1] = v.y; old[s][2] = v.z; old[s][V - 1] = v.w;
+            } else {
+                old[s][0] = __ldcg(row + (size_t)s * lane_stride + c);
+            }
+        }
+        if (V == 4) {
+            const float4 v = load4_cg(yrow + c);
+            yv[0] = v.x; yv[1] = v.y; yv[2] = v.z; yv[V - 1] = v.w;
+        } else {
+            yv[0] = load1_cg(yrow + c);
+        }
+#pragma unroll
+        for (int x = 0; x < V; ++x) u[x] = 0.f;
+#pragma unroll 1
+        for (int q = 0; q < n_streams; ++q) {
+            float nv[V];
+#pragma unroll
+            for (int x = 0; x < V; ++x) {
+                float v = 0.f;
+#pragma unroll
+                for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                    if (s < n_streams) v = fmaf(m[s * n_streams + q], old[s][x], v);
+                nv[x] = fmaf(b[q], yv[x], v);
+                u[x] = fmaf(a[q], nv[x], u[x]);
+            }
+            if (V == 4) store4(row + (size_t)q * lane_stride + c, make_float4(nv[0], nv[1], nv[2], nv[V - 1]));
+            else row[(size_t)q * lane_stride + c] = nv[0];
+        }
+#pragma unroll
+        for (int x = 0; x < V; ++x) ss = fmaf(u[x], u[x], ss);
+        if (V == 4) store4(dst + c, make_float4(u[0], u[1], u[2], u[V - 1]));
+        else dst[c] = u[0];
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+    for (int c = threadIdx.x * V; c < width; c += HC_THREADS * V) {
+        if (V == 4) {
+            float4 u = load4(dst + c);
+            const float4 g = *reinterpret_cast<const float4*>(gain + c);
+            u.x *= inv * g.x; u.y *= inv * g.y; u.z *= inv * g.z; u.w *= inv * g.w;
+            store4(dst + c, u);
+        } else {
+            dst[c] = dst[c] * inv * gain[c];
+        }
+    }
+}
+
+// y_dtype: 0 float, 1 bfloat16
+ST_EXPORT int st_hc_write_read_norm(float* lanes, int n_streams, const float* mix, const float* outc, const void* y,
+                                    int y_dtype, const float* coef, const float* gain, float eps, int n_tokens, int width,
+                                    float* out, const int* positions, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_streams <= 0 || width <= 0) return ST_ERR_BAD_ARG;
+    if (n_streams > HC_MAX_STREAMS) return ST_ERR_TOO_LARGE;
+    const long long stride = (long long)n_tokens * width;
+    const bool vec = width % 4 == 0 && aligned16(lanes) && aligned16(y) && aligned16(out) && aligned16(gain);
+    cudaStream_t s = (cudaStream_t)stream;
+#define HCWR(TY, V)                                                                                                   \
+    return st_launch_pdl("hc_write_read", hc_write_read_norm_kernel<TY, V>, dim3(n_tokens), dim3(HC_THREADS), 0, s,   \
+                         lanes, stride, n_streams, mix, outc, (const TY*)y, coef, gain, eps, width, out, positions)
+    if (y_dtype == 0) { if (vec) HCWR(float, 4); HCWR(float, 1); }
+    if (y_dtype == 1) { if (vec) HCWR(bf16, 4); HCWR(bf16, 1); }
+#undef HCWR
+    return ST_ERR_BAD_DTYPE;
 }
 
 ST_EXPORT int st_hc_spread(const float* x, float* lanes, long long n_elems, int n_streams, void* stream) {

@@ -1460,3 +1460,20 @@ def talk_attention_single(q: torch.Tensor, pool: torch.Tensor, layer: int, out: 
                                           gate_ptr, gate_ld, int(gate_heads), _f(out_scale), _p(scratch), int(n_cap),
                                           _p(status), _stream()), "talk_attention_single")
     return out
+
+
+def hc_write_read_norm(lanes: torch.Tensor, mix: torch.Tensor, out_coef: torch.Tensor, y: torch.Tensor,
+                       coef: torch.Tensor, gain: torch.Tensor, eps: float,
+                       positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hc_write(lanes, mix, out_coef, y)`` followed by ``hc_read_norm(lanes, coef, gain, eps)`` in one pass over the
+    streams: the update of the sub-layer that just ran and the read of the next one.  Rows of padding tokens
+    (negative position) are neither updated nor read."""
+    n, tokens, width = lanes.shape
+    assert lanes.dtype == torch.float32 and lanes.is_contiguous() and y.is_contiguous() and y.shape == (tokens, width)
+    assert mix.dtype == torch.float32 and mix.shape == (n, n) and mix.is_contiguous()
+    assert out_coef.dtype == torch.float32 and out_coef.numel() == n
+    assert coef.dtype == torch.float32 and coef.numel() == n and gain.dtype == torch.float32 and gain.numel() == width
+    out = torch.empty((tokens, width), dtype=torch.float32, device=lanes.device)
+    _check(lib().st_hc_write_read_norm(_p(lanes), n, _p(mix), _p(out_coef), _p(y), _dt(y), _p(coef), _p(gain), _f(eps),
+                                       tokens, width, _p(out), _p(positions), _stream()), "hc_write_read_norm")
+    return out

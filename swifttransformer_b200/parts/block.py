@@ -40,11 +40,21 @@ class ResidualStream:
     x0: Optional[torch.Tensor] = None      # the embedding's rows in the activation dtype (models that ask for them)
     turn: int = 0                          # which pass over a stretch of shared layers the running step belongs to
     lanes: Optional[torch.Tensor] = None   # [n, N, width] float32: the copies of a model with several residual streams
+    # (mix [n, n], out [n], y [N, width]): the update of the copies that the last sub-layer left to the next reader
+    lanes_pending: Optional[tuple] = None
+
+    def settle_lanes(self) -> None:
+        """Apply the update of the copies that the last sub-layer left pending."""
+        if self.lanes_pending is not None:
+            mix, out, y = self.lanes_pending
+            ops.hc_write(self.lanes, mix, out, y)
+            self.lanes_pending = None
 
     def fold(self) -> None:
         """A model with several residual streams: x <- their sum (what the final norm and the tools that look at
         the residual rows read); the copies themselves stay as they are."""
         if self.lanes is not None:
+            self.settle_lanes()
             ops.hc_sum(self.lanes, out=self.x)
             self.pending, self.act = None, None
 
@@ -243,7 +253,8 @@ class HyperPreNormBlock(Block):
     [n] and ``<hc>.mix`` [n, n] (indexed [from, to]):
 
         u = sum_s in[s] x_s;   h = norm(u);   h <- h + conv(h) (``canon_names``: a filter [width, taps] per
-        sub-layer, or None);   y = sub-layer(h);   x_t <- sum_s mix[s, t] x_s + out[t] y   for all t at once.
+        sub-layer, or None);   y = sub-layer(h);   x_t <- sum_s mix[s, t] x_s + out[t] y   for all t at once.  The update is left pending
+        (``ResidualStream.lanes_pending``) and done by the kernel that reads the copies next, in the same pass.
 
     The copies start as the embedding's rows (made by the first block that runs) and ``ResidualStream.fold`` sums
     them.  Mixture, norm statistics, the convolution and the update are float arithmetic on float rows; the
@@ -297,7 +308,13 @@ class HyperPreNormBlock(Block):
 
     def _input(self, i: int, stream: ResidualStream, norm: Norm, ctx: Any, tail: Any) -> torch.Tensor:
         a, _, _ = self.coef[i]
-        h = ops.hc_read_norm(stream.lanes, a, norm.gamma, norm.eps, ctx.positions)
+        if stream.lanes_pending is not None:
+            # the update the sub-layer before left pending and this read in one pass over the copies
+            mix, out_coef, y = stream.lanes_pending
+            stream.lanes_pending = None
+            h = ops.hc_write_read_norm(stream.lanes, mix, out_coef, y, a, norm.gamma, norm.eps, ctx.positions)
+        else:
+            h = ops.hc_read_norm(stream.lanes, a, norm.gamma, norm.eps, ctx.positions)
         out = torch.empty(h.shape, dtype=stream.act_dtype, device=h.device)
         if self.canon_names is None:
             if stream.act_dtype == torch.float32:
@@ -328,9 +345,10 @@ class HyperPreNormBlock(Block):
         tail1, mixer_cache, tail2 = cache
         h = self._input(0, stream, self.norm1, ctx, tail1)
         y = self._rows(self.mixer.forward(h, ctx, mixer_cache), stream)
-        ops.hc_write(stream.lanes, self.coef[0][1], self.coef[0][2], y)
+        # the update of the copies is left to the next reader (the next sub-layer's read, or ``fold``)
+        stream.lanes_pending = (self.coef[0][1], self.coef[0][2], y)
         if self.feed_forward is not None:
             h = self._input(1, stream, self.norm2, ctx, tail2)
             y = self._rows(self.feed_forward.forward(h, ctx), stream)
-            ops.hc_write(stream.lanes, self.coef[1][1], self.coef[1][2], y)
+            stream.lanes_pending = (self.coef[1][1], self.coef[1][2], y)
         stream.pending, stream.act = None, None

@@ -90,6 +90,19 @@ def test_streams_read_and_write(n, width):
         ops.hc_write(lanes, dev(w["hc.mix"]), dev(w["hc.out"]), dev(y, ydt))
         ref = pn.streams_update(xs, y, w, "hc")
         assert np.abs(lanes.cpu().numpy() - ref).max() < 1e-5 * np.abs(ref).max()
+    # the update and the next sub-layer's read in one pass: the same copies and the same normed mixture; the padding
+    # token's row is left alone
+    w2 = {"hc.in": rng.normal(size=n), "norm": 1 + 0.1 * rng.normal(size=width)}
+    for ydt in (torch.float32, torch.bfloat16):
+        y = bf16_round(rng.normal(size=(T, width)))
+        lanes = dev(xs)
+        h = ops.hc_write_read_norm(lanes, dev(w["hc.mix"]), dev(w["hc.out"]), dev(y, ydt), dev(w2["hc.in"]), dev(w2["norm"]),
+                                   1e-3, ints(pos)).cpu().numpy()
+        new = pn.streams_update(xs, y, w, "hc")
+        got = lanes.cpu().numpy()
+        assert np.abs(got[:, :T - 1] - new[:, :T - 1]).max() < 1e-5 * np.abs(new).max() and np.array_equal(got[:, T - 1], xs[:, T - 1].astype(np.float32))
+        ref = pn.sublayer_input(new, w2, "hc", "norm", "none", 1e-3)
+        assert np.abs(h[:T - 1] - ref[:T - 1]).max() < 2e-5 * np.abs(ref).max()
     # a mixing matrix that swaps two copies shows an update that reads a copy it has already written
     if n >= 2:
         swap = np.ascontiguousarray(np.eye(n)[:, [1, 0] + list(range(2, n))])
