@@ -9,6 +9,8 @@
 // hc_write_read_norm does the update of one sub-layer and the read of the next in one pass over the copies (a block per
 // token: the new values are written back and their mixture is normed while they are still in registers).
 //
+// hc_step_conv does all of that and the sub-layer's input convolution for steps in which every request brings one token.
+//
 // hc_spread makes the n copies of the embedding's rows, hc_sum adds them up at the end.  a, b [n] and M [n][n]
 // (indexed [from][to]) are float vectors on the device.
 //
@@ -217,6 +219,100 @@ ST_EXPORT int st_hc_write_read_norm(float* lanes, int n_streams, const float* mi
     if (y_dtype == 0) { if (vec) HCWR(float, 4); HCWR(float, 1); }
     if (y_dtype == 1) { if (vec) HCWR(bf16, 4); HCWR(bf16, 1); }
 #undef HCWR
+    return ST_ERR_BAD_DTYPE;
+}
+
+// Steps in which every request brings one token: update (y != null), read, norm and the input convolution in one
+// kernel, a block per token.  h = norm(u); out_act = h + sum_j w[c][j] * (the request's last taps - 1 inputs, h); the
+// state moves on by h.  A thread owns its channels of the request's state: conv_state float [slots][taps - 1][width].
+#define HC_MAX_TAPS 8
+#define HC_STEP_THREADS 1024     // such a step has few tokens, so few blocks: a block's threads are its parallelism
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(HC_STEP_THREADS)
+hc_step_conv_kernel(float* __restrict__ lanes, long long lane_stride, int n_streams, const float* __restrict__ mix,
+                    const float* __restrict__ outc, const TY* __restrict__ y, const float* __restrict__ coef,
+                    const float* __restrict__ gain, float eps, int width, const float* __restrict__ conv_w, int taps,
+                    float* __restrict__ conv_state, int write_state, float* __restrict__ tmp, TO* __restrict__ out_act,
+                    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                    const int* __restrict__ slots) {
+    __shared__ float m[HC_MAX_STREAMS * HC_MAX_STREAMS], b[HC_MAX_STREAMS], a[HC_MAX_STREAMS];
+    __shared__ float scratch[32];
+    if (y && threadIdx.x < n_streams * n_streams) m[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < n_streams) { b[threadIdx.x] = y ? outc[threadIdx.x] : 0.f; a[threadIdx.x] = coef[threadIdx.x]; }
+    __syncthreads();
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int t = blockIdx.x;
+    if (positions[t] < 0) return;
+    float* row = lanes + (size_t)t * width;
+    float* dst = tmp + (size_t)t * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += HC_STEP_THREADS) {
+        float old[HC_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s) old[s] = s < n_streams ? __ldcg(row + (size_t)s * lane_stride + c) : 0.f;
+        float u = 0.f;
+        if (y) {
+            const float yv = load1_cg(y + (size_t)t * width + c);
+#pragma unroll 1
+            for (int q = 0; q < n_streams; ++q) {
+                float v = 0.f;
+#pragma unroll
+                for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                    if (s < n_streams) v = fmaf(m[s * n_streams + q], old[s], v);
+                v = fmaf(b[q], yv, v);
+                row[(size_t)q * lane_stride + c] = v;
+                u = fmaf(a[q], v, u);
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                if (s < n_streams) u = fmaf(a[s], old[s], u);
+        }
+        ss = fmaf(u, u, ss);
+        dst[c] = u;
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+    const int keep = taps - 1;
+    float* st = conv_state + (size_t)slots[seq_of_token[t]] * keep * width;
+    for (int c = threadIdx.x; c < width; c += HC_STEP_THREADS) {
+        const float h = dst[c] * inv * gain[c];
+        float vv[HC_MAX_TAPS];
+        float o = h;
+        for (int j = 0; j < keep; ++j) {
+            vv[j] = __ldcg(st + (size_t)j * width + c);
+            o = fmaf(conv_w[(size_t)c * taps + j], vv[j], o);
+        }
+        o = fmaf(conv_w[(size_t)c * taps + keep], h, o);
+        if (write_state) {
+            for (int j = 0; j + 1 < keep; ++j) st[(size_t)j * width + c] = vv[j + 1];
+            if (keep > 0) st[(size_t)(keep - 1) * width + c] = h;
+        }
+        out_act[(size_t)t * width + c] = from_f32<TO>(o);
+    }
+}
+
+// y null: no update, read only.  y_dtype / out_dtype: 0 float, 1 bfloat16.  tmp: float [n_tokens][width] scratch.
+ST_EXPORT int st_hc_step_conv(float* lanes, int n_streams, const float* mix, const float* outc, const void* y, int y_dtype,
+                              const float* coef, const float* gain, float eps, int n_tokens, int width,
+                              const float* conv_w, int taps, float* conv_state, int write_state, float* tmp,
+                              void* out_act, int out_dtype, const int* positions, const int* seq_of_token,
+                              const int* slots, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_streams <= 0 || width <= 0 || taps < 1 || !positions || !seq_of_token || !slots) return ST_ERR_BAD_ARG;
+    if (n_streams > HC_MAX_STREAMS || taps > HC_MAX_TAPS) return ST_ERR_TOO_LARGE;
+    const long long stride = (long long)n_tokens * width;
+    cudaStream_t s = (cudaStream_t)stream;
+#define HCSC(TY, TO)                                                                                                  \
+    return st_launch_pdl("hc_step_conv", hc_step_conv_kernel<TY, TO>, dim3(n_tokens), dim3(HC_STEP_THREADS), 0, s, lanes, \
+                         stride, n_streams, mix, outc, (const TY*)y, coef, gain, eps, width, conv_w, taps, conv_state, \
+                         write_state, tmp, (TO*)out_act, positions, seq_of_token, slots)
+    const int yd = y ? y_dtype : 0;
+    if (yd == 0 && out_dtype == 0) HCSC(float, float);
+    if (yd == 0 && out_dtype == 1) HCSC(float, bf16);
+    if (yd == 1 && out_dtype == 0) HCSC(bf16, float);
+    if (yd == 1 && out_dtype == 1) HCSC(bf16, bf16);
+#undef HCSC
     return ST_ERR_BAD_DTYPE;
 }
 

@@ -1477,3 +1477,28 @@ def hc_write_read_norm(lanes: torch.Tensor, mix: torch.Tensor, out_coef: torch.T
     _check(lib().st_hc_write_read_norm(_p(lanes), n, _p(mix), _p(out_coef), _p(y), _dt(y), _p(coef), _p(gain), _f(eps),
                                        tokens, width, _p(out), _p(positions), _stream()), "hc_write_read_norm")
     return out
+
+
+def hc_step_conv(lanes: torch.Tensor, pending: Optional[tuple], coef: torch.Tensor, gain: torch.Tensor, eps: float,
+                 conv_w: torch.Tensor, conv_state: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                 seq_of_token: torch.Tensor, slots: torch.Tensor, write_state: bool = True) -> torch.Tensor:
+    """For steps in which every request brings one token: the pending update of the streams (``pending`` = (mix,
+    out_coef, y) or None), the next sub-layer's read and norm, and its input convolution h + conv(h) over the request's
+    last taps - 1 inputs (``conv_state`` float32 [slots, taps - 1, width], moved on by h), in one kernel.  ``out``
+    [tokens, width] in the activation type receives the sub-layer's input."""
+    n, tokens, width = lanes.shape
+    taps = conv_w.shape[1]
+    assert lanes.dtype == torch.float32 and lanes.is_contiguous() and out.is_contiguous() and out.shape == (tokens, width)
+    assert conv_w.dtype == torch.float32 and conv_w.shape == (width, taps) and conv_w.is_contiguous()
+    assert conv_state.dtype == torch.float32 and conv_state.is_contiguous() and conv_state.shape[1:] == (taps - 1, width)
+    assert coef.dtype == torch.float32 and coef.numel() == n and gain.dtype == torch.float32 and gain.numel() == width
+    mix = out_coef = y = None
+    if pending is not None:
+        mix, out_coef, y = pending
+        assert y.is_contiguous() and y.shape == (tokens, width) and mix.shape == (n, n) and out_coef.numel() == n
+    tmp = torch.empty((tokens, width), dtype=torch.float32, device=lanes.device)
+    _check(lib().st_hc_step_conv(_p(lanes), n, _p(mix), _p(out_coef), _p(y), _dt(y) if y is not None else 0, _p(coef),
+                                 _p(gain), _f(eps), tokens, width, _p(conv_w), taps, _p(conv_state), int(write_state),
+                                 _p(tmp), _p(out), _dt(out), _p(positions), _p(seq_of_token), _p(slots), _stream()),
+           "hc_step_conv")
+    return out

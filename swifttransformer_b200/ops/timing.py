@@ -24,7 +24,7 @@ TIMED = ("embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gathe
          "diff_qkv_prepare", "diff_attention_plain", "diff_attention_single", "diff_attention_tiles", "hgrn2_scan",
          "latent_prepare", "latent_q_rotate", "latent_attention", "gemm_heads", "moe_route", "moe_sort", "gemm_experts",
          "moe_combine", "concat_rows", "scale_softcap", "gqa_prepare", "gqa_attention_plain", "gqa_attention_single",
-         "gqa_attention_tiles", "delta_rule", "gated_clamped_act", "hc_spread", "hc_sum", "hc_read_norm", "hc_write", "hc_write_read_norm",
+         "gqa_attention_tiles", "delta_rule", "gated_clamped_act", "hc_spread", "hc_sum", "hc_read_norm", "hc_write", "hc_write_read_norm", "hc_step_conv",
          "norm_pair_sum", "xielu", "talk_attention_plain", "talk_attention_tiles", "talk_attention_single")
 
 _originals: Dict[str, object] = {}

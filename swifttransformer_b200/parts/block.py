@@ -308,6 +308,12 @@ class HyperPreNormBlock(Block):
 
     def _input(self, i: int, stream: ResidualStream, norm: Norm, ctx: Any, tail: Any) -> torch.Tensor:
         a, _, _ = self.coef[i]
+        if self.canon_names is not None and tail is not None and getattr(ctx, "single_tokens", False):
+            # every request brings one token: pending update, read, norm and convolution in one kernel
+            out = torch.empty(stream.x.shape, dtype=stream.act_dtype, device=stream.x.device)
+            pending, stream.lanes_pending = stream.lanes_pending, None
+            return ops.hc_step_conv(stream.lanes, pending, a, norm.gamma, norm.eps, self.filters[i], tail.state, out,
+                                    ctx.positions, ctx.seq_of_token, ctx.slots, write_state=tail.writable)
         if stream.lanes_pending is not None:
             # the update the sub-layer before left pending and this read in one pass over the copies
             mix, out_coef, y = stream.lanes_pending

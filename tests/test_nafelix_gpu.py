@@ -117,6 +117,43 @@ def test_streams_read_and_write(n, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,width,taps", [(3, 44, 2), (4, 64, 5), (1, 20, 3)])
+def test_single_token_steps_update_read_norm_and_convolve_in_one_kernel(dtype, n, width, taps):
+    """Three requests decoded side by side for several steps through ``hc_step_conv`` (with and without a pending
+    update), a padding token beside them: the sub-layer's input equals norm + convolution of the plain functions over
+    each request's whole history, and the states of other slots are left alone."""
+    from swifttransformer_b200 import ops
+    rng = np.random.default_rng(n * width + taps)
+    B, steps, slots = 3, 7, [2, 0, 3]
+    w = {"hc.in": rng.normal(size=n), "hc.mix": np.eye(n) + 0.2 * rng.normal(size=(n, n)), "hc.out": 1 + 0.2 * rng.normal(size=n),
+         "norm": 1 + 0.1 * rng.normal(size=width), "canon": rng.normal(size=(width, taps)) * 0.5}
+    state = torch.zeros((5, taps - 1, width), device="cuda")
+    state[1] = 7.0
+    xs = rng.normal(size=(steps, n, B, width))            # the copies' rows each step brings (before the update)
+    ys = bf16_round(rng.normal(size=(steps, B, width)))
+    hist = [[] for _ in range(B)]
+    for k in range(steps):
+        lanes = dev(np.concatenate([xs[k], np.full((n, 1, width), 3.0)], axis=1))
+        st = Step([(slots[b], k, 1) for b in range(B)], pad_tokens=1)
+        pending = None if k % 3 == 0 else (dev(w["hc.mix"]), dev(w["hc.out"]), dev(np.concatenate([ys[k], np.zeros((1, width))]), TD[dtype]))
+        out = torch.full((B + 1, width), 5.0, dtype=TD[dtype], device="cuda")
+        ops.hc_step_conv(lanes, pending, dev(w["hc.in"]), dev(w["norm"]), 1e-4, dev(w["canon"]), state, out, st.positions,
+                         st.seq, st.slots)
+        new = pn.streams_update(xs[k], ys[k], w, "hc") if pending is not None else xs[k]
+        assert np.abs(lanes.cpu().numpy()[:, :B] - new).max() < 1e-5 * np.abs(new).max()
+        assert np.all(lanes.cpu().numpy()[:, B] == 3.0) and np.all(out.float().cpu().numpy()[B] == 5.0)
+        got = out.float().cpu().numpy()
+        for b in range(B):
+            u = np.einsum("s,sw->w", w["hc.in"], new[:, b])
+            hist[b].append(pn.rms_unit(u, 1e-4) * w["norm"])
+            h = np.stack(hist[b])
+            ref = (h + pn.causal_conv(h, w["canon"]))[-1]
+            tol = 2e-5 if dtype == "float32" else 1e-2
+            assert np.abs(got[b] - ref).max() < tol * np.abs(ref).max(), (k, b)
+    assert torch.all(state[1] == 7.0) and float(state[4].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_pair_of_normed_results_and_two_sided_activation(dtype):
     from swifttransformer_b200 import ops
     rng = np.random.default_rng(4)
